@@ -24,7 +24,7 @@ import torch
 
 from .. import kernels
 from .allocators import CacheError, CacheFull, IndexAllocator
-from .spec import PAGE_TOKENS, FixedStateSpec, KVStateSpec
+from .spec import PAGE_TOKENS, CompositeStateSpec, FixedStateSpec, KVStateSpec
 
 DEFAULT_MAX_SEQS = 4096
 
@@ -129,6 +129,15 @@ class FixedView:
     unit: int = -1
 
 
+@dataclasses.dataclass
+class CompositeView:
+    """What a layer with several mixers side by side gets: one view per mixer, in their order."""
+    spec: CompositeStateSpec
+    views: list
+    owned: bool = True
+    unit: int = -1
+
+
 class Cache:
     """Device storage for a list of state specs (one per state unit of the model's plan)."""
 
@@ -138,10 +147,7 @@ class Cache:
         kv_groups, fixed_groups = [], []
         self._where = []                                   # state unit -> (kind, group, index)
         counts = {}
-        for spec in self.state_specs:
-            if spec is None:
-                self._where.append(None)
-                continue
+        def place(spec):
             table = kv_groups if isinstance(spec, KVStateSpec) else fixed_groups
             if spec not in table:
                 table.append(spec)
@@ -149,7 +155,15 @@ class Cache:
             kind = "kv" if isinstance(spec, KVStateSpec) else "fixed"
             idx = counts.get((kind, g), 0)
             counts[(kind, g)] = idx + 1
-            self._where.append((kind, g, idx))
+            return (kind, g, idx)
+
+        for spec in self.state_specs:
+            if spec is None:
+                self._where.append(None)
+            elif isinstance(spec, CompositeStateSpec):
+                self._where.append(("composite", spec, [place(p) for p in spec.parts]))
+            else:
+                self._where.append(place(spec))
         self.book = CacheBook(kv_groups, max_tokens, max_seqs, max_len)
         self.kv_storage, self.ptabs, self._ptab_offset = [], [], []
         total_entries = sum(self.book.max_seqs * p for p in self.book.pages_per_seq)
@@ -177,6 +191,11 @@ class Cache:
         where = self._where[unit]
         if where is None:
             return None
+        if where[0] == "composite":
+            return CompositeView(where[1], [self._view_of(w) for w in where[2]])
+        return self._view_of(where)
+
+    def _view_of(self, where):
         kind, g, idx = where
         if kind == "kv":
             return KVView(self.kv_specs[g], self.kv_storage[g][idx], self.book.group_pages[g], self.ptabs[g], g)

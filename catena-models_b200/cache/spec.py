@@ -10,6 +10,10 @@ an equal spec into one group with storage of its own:
 * `FixedStateSpec(shape, dtype)`: a constant number of bytes per sequence, whatever its
   length, like the short convolution's last L_cache-1 inputs (src/lfm3.rs:309, 327, 365).
 
+* `CompositeStateSpec(parts)`: a layer whose mixer is made of several mixers side by side keeps each
+  one's state; the cache stores every part in the group of its own kind and hands the layer one view
+  per part.
+
 A spec also says how the launches of a decode step depend on the sequences' length
 (`length_class`), which is all the engine needs to know to decide which recorded step may be
 replayed; a mixer sizes its launches from the same answer.  A spec class of another mixer
@@ -63,3 +67,11 @@ class FixedStateSpec:
     def length_class(self, length):
         """A state of fixed size is handled the same way at every length: one class."""
         return 0
+
+
+@dataclasses.dataclass(frozen=True)
+class CompositeStateSpec:
+    parts: tuple               # KVStateSpec | FixedStateSpec, one per mixer of the layer, in the mixers' order
+
+    def length_class(self, length):
+        return tuple(p.length_class(length) for p in self.parts)

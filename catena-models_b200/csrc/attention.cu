@@ -27,6 +27,13 @@ __device__ __forceinline__ void load8<bf16>(const bf16* p, float* out) {
     }
 }
 
+// Query temperature: queries at position p are multiplied by 1 + coef * ln(floor((p + 1) / every) + 1),
+// a factor that grows with the logarithm of the position in steps of `every` tokens (every <= 0: none).
+__device__ __forceinline__ float query_temperature(int pos, float coef, int every) {
+    if (every <= 0) return 1.f;
+    return 1.f + coef * logf((float)((pos + 1) / every) + 1.f);
+}
+
 // =========================================================================================
 // Head norm, rotation, cache write.  One warp per (token, head); q heads first, then k heads.
 //   qkv row: [ q: QH*HD | k: KVH*HD | v: KVH*HD | ... ]  (row stride ld)
@@ -47,7 +54,7 @@ __global__ void qk_prepare_kernel(T* __restrict__ qkv, long long ld, const float
                                   const int* __restrict__ seq_slot, const int* __restrict__ seq_end,
                                   T* __restrict__ pool, long long pages, const int* __restrict__ ptab,
                                   int ptab_stride, int ring, int QH, int KVH, int HD, float eps, int T_tokens,
-                                  int heads_per_warp, int interleaved) {
+                                  int heads_per_warp, int interleaved, float qt_coef, int qt_every) {
     pdl_trigger();
     pdl_wait();
     // One warp per token and group of `heads_per_warp` heads (grid.y walks the groups: many heads
@@ -60,6 +67,7 @@ __global__ void qk_prepare_kernel(T* __restrict__ qkv, long long ld, const float
     if (t >= T_tokens || tok_seq[t] < 0) return;      // a row of padding belongs to no sequence
     const int pos = tok_pos[t];
     const int half = HD >> 1;
+    const float q_temp = query_temperature(pos, qt_coef, qt_every);
     float sn[MAXP], cs[MAXP];
 #pragma unroll
     for (int p = 0; p < MAXP; ++p) {
@@ -112,6 +120,10 @@ __global__ void qk_prepare_kernel(T* __restrict__ qkv, long long ld, const float
                 a = rounded<T>((a * inv) * w[i_lo]);
                 bq = rounded<T>((bq * inv) * w[i_hi]);
             }
+            if (is_q) {
+                a *= q_temp;
+                bq *= q_temp;
+            }
             const T at = from_f32<T>(a * cs[p] - bq * sn[p]), bt = from_f32<T>(bq * cs[p] + a * sn[p]);
             x[i_lo] = at;
             x[i_hi] = bt;
@@ -143,7 +155,7 @@ qk_prepare_vec_kernel(T* __restrict__ qkv, long long ld, const float* __restrict
                       const int* __restrict__ seq_slot, const int* __restrict__ seq_end,
                       T* __restrict__ pool, long long pages, const int* __restrict__ ptab,
                       int ptab_stride, int ring, int QH, int KVH, int HD, float eps, int T_tokens,
-                      int passes_per_warp) {
+                      int passes_per_warp, float qt_coef, int qt_every) {
     pdl_trigger();
     pdl_wait();
     const int lane = threadIdx.x;
@@ -152,6 +164,7 @@ qk_prepare_vec_kernel(T* __restrict__ qkv, long long ld, const float* __restrict
     const int half = HD >> 1, LPH = half >> 3, HPP = 32 / LPH;
     const int sub = lane % LPH, hsel = lane / LPH;          // lanes past HPP * LPH idle along
     const int pos = tok_pos[t];
+    const float q_temp = query_temperature(pos, qt_coef, qt_every);
     float sn[8], cs[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
@@ -201,6 +214,13 @@ qk_prepare_vec_kernel(T* __restrict__ qkv, long long ld, const float* __restrict
                 hi[e] = rounded<T>((hi[e] * inv) * wh[e]);
             }
         }
+        if (is_q) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                lo[e] *= q_temp;
+                hi[e] *= q_temp;
+            }
+        }
         float ol[8], oh[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
@@ -231,7 +251,7 @@ extern "C" int cm_qk_prepare(int dt, void* qkv, long long ld, const float* wq, c
                              const float* rate, const int* tok_pos, const int* tok_seq,
                              const int* seq_slot, const int* seq_end, void* pool, long long pages,
                              const int* ptab, int ptab_stride, int ring, int T, int QH, int KVH,
-                             int HD, float eps, int interleaved, cudaStream_t st) {
+                             int HD, float eps, int interleaved, float qt_coef, int qt_every, cudaStream_t st) {
     if (T <= 0) return CM_OK;
     if (HD % 2 || HD <= 0) CM_REFUSE("qk_prepare: head size %d is not even", HD);
     if (ring % PAGE_TOKENS) CM_REFUSE("qk_prepare: ring of %d entries is no multiple of %d", ring, PAGE_TOKENS);
@@ -250,10 +270,10 @@ extern "C" int cm_qk_prepare(int dt, void* qkv, long long ld, const float* wq, c
         dim3 vblock(32, 4), vgrid((T + 3) / 4, (passes + ppw - 1) / ppw);
         if (dt == DT_F32)
             cm_launch(qk_prepare_vec_kernel<float>, vgrid, vblock, 0, st, (float*)qkv, ld, wq, wk, rate, tok_pos, tok_seq,
-                      seq_slot, seq_end, (float*)pool, pages, ptab, ptab_stride, ring, QH, KVH, HD, eps, T, ppw);
+                      seq_slot, seq_end, (float*)pool, pages, ptab, ptab_stride, ring, QH, KVH, HD, eps, T, ppw, qt_coef, qt_every);
         else
             cm_launch(qk_prepare_vec_kernel<bf16>, vgrid, vblock, 0, st, (bf16*)qkv, ld, wq, wk, rate, tok_pos, tok_seq,
-                      seq_slot, seq_end, (bf16*)pool, pages, ptab, ptab_stride, ring, QH, KVH, HD, eps, T, ppw);
+                      seq_slot, seq_end, (bf16*)pool, pages, ptab, ptab_stride, ring, QH, KVH, HD, eps, T, ppw, qt_coef, qt_every);
         CM_CHECK_LAUNCH();
         return CM_OK;
     }
@@ -263,11 +283,11 @@ extern "C" int cm_qk_prepare(int dt, void* qkv, long long ld, const float* wq, c
     if (dt == DT_F32)
         cm_launch(qk_prepare_kernel<float>, grid, block, smem, st, (float*)qkv, ld, wq, wk, rate, tok_pos, tok_seq,
                                                             seq_slot, seq_end, (float*)pool, pages, ptab,
-                                                            ptab_stride, ring, QH, KVH, HD, eps, T, hpw, interleaved);
+                                                            ptab_stride, ring, QH, KVH, HD, eps, T, hpw, interleaved, qt_coef, qt_every);
     else if (dt == DT_BF16)
         cm_launch(qk_prepare_kernel<bf16>, grid, block, smem, st, (bf16*)qkv, ld, wq, wk, rate, tok_pos, tok_seq,
                                                            seq_slot, seq_end, (bf16*)pool, pages, ptab,
-                                                           ptab_stride, ring, QH, KVH, HD, eps, T, hpw, interleaved);
+                                                           ptab_stride, ring, QH, KVH, HD, eps, T, hpw, interleaved, qt_coef, qt_every);
     else
         return CM_ERR_DTYPE;
     CM_CHECK_LAUNCH();
@@ -299,7 +319,7 @@ attn_prefill_simt_kernel(T* __restrict__ ctx, long long ldc, const T* __restrict
                          const int* __restrict__ seq_start, int QH, int KVH, int HD, int window,
                          float scale, const int* __restrict__ seq_pos0, const int* __restrict__ seq_slot,
                          const T* __restrict__ pool, long long pages, const int* __restrict__ ptab,
-                         int ptab_stride, int ring) {
+                         int ptab_stride, int ring, const float* __restrict__ sink) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float smem[];
@@ -404,7 +424,7 @@ attn_prefill_simt_kernel(T* __restrict__ ctx, long long ldc, const T* __restrict
         const long long t = s0 + q0 - p0 + qi;
         float g = 1.f;
         if (gate) g = sigmoid_f32(to_f32(gate[t * ldg + hq]));
-        const float inv = 1.f / l[i];
+        const float inv = 1.f / (l[i] + (sink ? expf(sink[hq] - m[i]) : 0.f));   // a sink joins the denominator only
 #pragma unroll
         for (int j = 0; j < AP_MAXJ; ++j) {
             const int d = lane + 32 * j;
@@ -417,13 +437,13 @@ template <typename T, bool PAST>
 static int launch_attn_simt(void* ctx, long long ldc, const void* q, const void* k, const void* v, long long ld,
                             const void* gate, long long ldg, const int* seq_start, int B, int max_len, int QH, int KVH,
                             int HD, int window, float scale, const int* seq_pos0, const int* seq_slot, const void* pool,
-                            long long pages, const int* ptab, int ptab_stride, int ring, cudaStream_t st) {
+                            long long pages, const int* ptab, int ptab_stride, int ring, const float* sink, cudaStream_t st) {
     const size_t smem = ((size_t)(AP_BQ + AP_BK) * (HD + 1) + (size_t)AP_BK * HD + AP_BQ * (AP_BK + 1)) * sizeof(float);
     dim3 grid((max_len + AP_BQ - 1) / AP_BQ, QH, B);
     cudaFuncSetAttribute(attn_prefill_simt_kernel<T, PAST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     cm_launch(attn_prefill_simt_kernel<T, PAST>, grid, 128, smem, st, (T*)ctx, ldc, (const T*)q, (const T*)k, (const T*)v,
               ld, (const T*)gate, ldg, seq_start, QH, KVH, HD, window, scale, seq_pos0, seq_slot, (const T*)pool, pages,
-              ptab, ptab_stride, ring);
+              ptab, ptab_stride, ring, sink);
     CM_CHECK_LAUNCH();
     return CM_OK;
 }
@@ -431,16 +451,16 @@ static int launch_attn_simt(void* ctx, long long ldc, const void* q, const void*
 extern "C" int cm_attn_prefill_simt(int dt, void* ctx, long long ldc, const void* q, const void* k,
                                     const void* v, long long ld, const void* gate, long long ldg,
                                     const int* seq_start, int B, int max_len, int QH, int KVH, int HD,
-                                    int window, float scale, cudaStream_t st) {
+                                    int window, float scale, const float* sink, cudaStream_t st) {
     if (B <= 0 || max_len <= 0) return CM_OK;
     if (HD > 32 * AP_MAXJ) CM_REFUSE("attn_prefill: head size %d above %d", HD, 32 * AP_MAXJ);
     if (QH % KVH) CM_REFUSE("attn_prefill: %d query heads over %d key heads", QH, KVH);
     if (dt == DT_F32)
         return launch_attn_simt<float, false>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, QH, KVH, HD, window,
-                                              scale, nullptr, nullptr, nullptr, 0, nullptr, 0, 0, st);
+                                              scale, nullptr, nullptr, nullptr, 0, nullptr, 0, 0, sink, st);
     if (dt == DT_BF16)
         return launch_attn_simt<bf16, false>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, QH, KVH, HD, window,
-                                             scale, nullptr, nullptr, nullptr, 0, nullptr, 0, 0, st);
+                                             scale, nullptr, nullptr, nullptr, 0, nullptr, 0, 0, sink, st);
     return CM_ERR_DTYPE;
 }
 
@@ -451,7 +471,8 @@ extern "C" int cm_attn_append_simt(int dt, void* ctx, long long ldc, const void*
                                    const void* v, long long ld, const void* gate, long long ldg,
                                    const int* seq_start, const int* seq_pos0, const int* seq_slot, const void* pool,
                                    long long pages, const int* ptab, long long ptab_stride, int ring, int B,
-                                   int max_len, int QH, int KVH, int HD, int window, float scale, cudaStream_t st) {
+                                   int max_len, int QH, int KVH, int HD, int window, float scale, const float* sink,
+                                   cudaStream_t st) {
     if (B <= 0 || max_len <= 0) return CM_OK;
     if (HD > 32 * AP_MAXJ) CM_REFUSE("attn_append: head size %d above %d", HD, 32 * AP_MAXJ);
     if (QH % KVH) CM_REFUSE("attn_append: %d query heads over %d key heads", QH, KVH);
@@ -459,10 +480,10 @@ extern "C" int cm_attn_append_simt(int dt, void* ctx, long long ldc, const void*
     if (!seq_pos0 || !seq_slot || !pool || !ptab) CM_REFUSE("attn_append: positions, slots, cache and page table are needed");
     if (dt == DT_F32)
         return launch_attn_simt<float, true>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, QH, KVH, HD, window,
-                                             scale, seq_pos0, seq_slot, pool, pages, ptab, (int)ptab_stride, ring, st);
+                                             scale, seq_pos0, seq_slot, pool, pages, ptab, (int)ptab_stride, ring, sink, st);
     if (dt == DT_BF16)
         return launch_attn_simt<bf16, true>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, QH, KVH, HD, window,
-                                            scale, seq_pos0, seq_slot, pool, pages, ptab, (int)ptab_stride, ring, st);
+                                            scale, seq_pos0, seq_slot, pool, pages, ptab, (int)ptab_stride, ring, sink, st);
     return CM_ERR_DTYPE;
 }
 
@@ -738,7 +759,7 @@ __global__ void attn_decode_merge_kernel(T* __restrict__ ctx, long long ldc,
                                          const float* __restrict__ part_ml,
                                          const T* __restrict__ gate, long long ldg,
                                          const int* __restrict__ seq_pos, int ring, int QH, int HD,
-                                         int n_chunks) {
+                                         int n_chunks, const float* __restrict__ sink) {
     pdl_trigger();
     pdl_wait();
     const int hq = blockIdx.x, b = blockIdx.y;
@@ -753,6 +774,7 @@ __global__ void attn_decode_merge_kernel(T* __restrict__ ctx, long long ldc,
         const float mc = part_ml[(base + c) * 2];
         den += mc == -INFINITY ? 0.f : part_ml[(base + c) * 2 + 1] * expf(mc - mx);
     }
+    if (sink) den += expf(sink[hq] - mx);          // the sink has no key and no value: it counts once, here
     float g = 1.f;
     if (gate) g = sigmoid_f32(to_f32(gate[(long long)b * ldg + hq]));
     for (int d = threadIdx.x; d < HD; d += blockDim.x) {
@@ -781,7 +803,7 @@ extern "C" int cm_attn_decode(int dt, void* ctx, long long ldc, const void* q, l
                               const void* gate, long long ldg, const int* seq_pos, const int* seq_slot,
                               const void* pool, long long pages, const int* ptab, int ptab_stride,
                               int ring, int window, int B, int QH, int KVH, int HD, int n_chunks,
-                              float scale, float* part_o, float* part_ml, cudaStream_t st) {
+                              float scale, float* part_o, float* part_ml, const float* sink, cudaStream_t st) {
     if (B <= 0) return CM_OK;
     if (HD % 8 || HD < 8 || HD > CM_MAX_HEAD_DIM)
         CM_REFUSE("attn_decode: head size %d (multiples of 8 up to %d)", HD, CM_MAX_HEAD_DIM);
@@ -816,17 +838,17 @@ extern "C" int cm_attn_decode(int dt, void* ctx, long long ldc, const void* q, l
                                                 &n_parts, st);
         if (rc != CM_OK) return rc;
         cm_launch(attn_decode_merge_kernel<bf16>, mgrid, mthreads, 0, st, (bf16*)ctx, ldc, part_o, part_ml,
-                  (const bf16*)gate, ldg, seq_pos, ring, QH, HD, n_parts);
+                  (const bf16*)gate, ldg, seq_pos, ring, QH, HD, n_parts, sink);
     } else if (dt == DT_F32) {
         AD_DISPATCH(float);
         CM_CHECK_LAUNCH();
         cm_launch(attn_decode_merge_kernel<float>, mgrid, mthreads, 0, st, (float*)ctx, ldc, part_o, part_ml,
-                  (const float*)gate, ldg, seq_pos, ring, QH, HD, n_chunks);
+                  (const float*)gate, ldg, seq_pos, ring, QH, HD, n_chunks, sink);
     } else if (dt == DT_BF16) {
         AD_DISPATCH(bf16);
         CM_CHECK_LAUNCH();
         cm_launch(attn_decode_merge_kernel<bf16>, mgrid, mthreads, 0, st, (bf16*)ctx, ldc, part_o, part_ml,
-                  (const bf16*)gate, ldg, seq_pos, ring, QH, HD, n_chunks);
+                  (const bf16*)gate, ldg, seq_pos, ring, QH, HD, n_chunks, sink);
     } else
         return CM_ERR_DTYPE;
 #undef AD_DISPATCH
@@ -891,5 +913,5 @@ extern "C" int cm_attn_decode_noalloc(int dt, void* ctx, long long ldc, const vo
     if (rc != CM_OK) return rc;
     // part_o first (16-byte aligned for any size since HD is a multiple of 8), then part_ml
     return cm_attn_decode(dt, ctx, ldc, q, ldq, gate, ldg, seq_pos, seq_slot, pool, pages, ptab, ptab_stride, ring,
-                          window, B, QH, KVH, HD, n_chunks, scale, scratch, scratch + o_floats, st);
+                          window, B, QH, KVH, HD, n_chunks, scale, scratch, scratch + o_floats, nullptr, st);
 }

@@ -63,7 +63,7 @@ attn_prefill_mma_kernel(bf16* __restrict__ ctx, long long ldc, const bf16* __res
                         const bf16* __restrict__ gate, long long ldg, const int* __restrict__ seq_start, int QH,
                         int KVH, int window, float scale_log2, const int* __restrict__ seq_pos0,
                         const int* __restrict__ seq_slot, const bf16* __restrict__ pool, long long pages,
-                        const int* __restrict__ ptab, int ptab_stride, int ring) {
+                        const int* __restrict__ ptab, int ptab_stride, int ring, const float* __restrict__ sink) {
     constexpr int LDS = HD + 8;                   // padded row, elements
     constexpr int CH = HD / 8;                    // 16-byte chunks per row
     extern __shared__ __align__(16) uint8_t fa_smem[];
@@ -266,7 +266,8 @@ attn_prefill_mma_kernel(bf16* __restrict__ ctx, long long ldc, const bf16* __res
         const int row = row_lo + 8 * h;
         if (row >= len) continue;
         const long long tok = s0 + row - p0;
-        float f = 1.f / l_run[h];
+        // a sink logit (natural units; the running maximum is in log2 units) joins the denominator only
+        float f = 1.f / (l_run[h] + (sink ? exp2f(sink[hq] * 1.4426950408889634f - m_run[h]) : 0.f));
         if (gate) f *= sigmoid_f32(__bfloat162float(gate[tok * ldg + hq]));
         bf16* dst = ctx + tok * ldc + (long long)hq * HD;
 #pragma unroll
@@ -283,6 +284,7 @@ struct FaPast {                      // where the keys and values below a sequen
     const int* ptab;
     int ptab_stride;
     int ring;
+    const float* sink;               // per query head, or null: a logit without key and value in the softmax's denominator
 };
 
 template <int HD, int BQ, bool PAST>
@@ -302,7 +304,7 @@ static int launch_fa_bq(void* ctx, long long ldc, const void* q, const void* k, 
     dim3 grid((max_len + BQ - 1) / BQ, QH, B);
     cm_launch(kernel, grid, BQ * 2, smem, st, (bf16*)ctx, ldc, (const bf16*)q, (const bf16*)k, (const bf16*)v, ld,
               (const bf16*)gate, ldg, seq_start, QH, KVH, window, scale * 1.4426950408889634f, past.seq_pos0,
-              past.seq_slot, (const bf16*)past.pool, past.pages, past.ptab, past.ptab_stride, past.ring);
+              past.seq_slot, (const bf16*)past.pool, past.pages, past.ptab, past.ptab_stride, past.ring, past.sink);
     CM_CHECK_LAUNCH();
     return CM_OK;
 }
@@ -343,9 +345,10 @@ static int dispatch_fa(void* ctx, long long ldc, const void* q, const void* k, c
 // buffer with a row pitch that is a multiple of 8 elements and 16-byte aligned bases.
 extern "C" int cm_attn_prefill_mma(void* ctx, long long ldc, const void* q, const void* k, const void* v,
                                    long long ld, const void* gate, long long ldg, const int* seq_start, int B,
-                                   int max_len, int QH, int KVH, int HD, int window, float scale, cudaStream_t st) {
+                                   int max_len, int QH, int KVH, int HD, int window, float scale, const float* sink,
+                                   cudaStream_t st) {
     if (B <= 0 || max_len <= 0) return CM_OK;
-    const FaPast none = {nullptr, nullptr, nullptr, 0, nullptr, 0, 0};
+    const FaPast none = {nullptr, nullptr, nullptr, 0, nullptr, 0, 0, sink};
     return dispatch_fa<false>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, QH, KVH, HD, window, scale, none, st);
 }
 
@@ -355,12 +358,12 @@ extern "C" int cm_attn_append_mma(void* ctx, long long ldc, const void* q, const
                                   long long ld, const void* gate, long long ldg, const int* seq_start,
                                   const int* seq_pos0, const int* seq_slot, const void* pool, long long pages,
                                   const int* ptab, long long ptab_stride, int ring, int B, int max_len, int QH, int KVH,
-                                  int HD, int window, float scale, cudaStream_t st) {
+                                  int HD, int window, float scale, const float* sink, cudaStream_t st) {
     if (B <= 0 || max_len <= 0) return CM_OK;
     if (ring % PAGE_TOKENS) CM_REFUSE("attn_append_mma: ring of %d entries is no multiple of %d", ring, PAGE_TOKENS);
     if (!seq_pos0 || !seq_slot || !pool || !ptab)
         CM_REFUSE("attn_append_mma: positions, slots, cache and page table are needed");
-    const FaPast past = {seq_pos0, seq_slot, pool, pages, ptab, (int)ptab_stride, ring};
+    const FaPast past = {seq_pos0, seq_slot, pool, pages, ptab, (int)ptab_stride, ring, sink};
     return dispatch_fa<true>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, QH, KVH, HD, window, scale, past, st);
 }
 

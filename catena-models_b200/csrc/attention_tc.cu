@@ -163,6 +163,7 @@ struct FtPast {                      // where the keys and values below a sequen
     long long ptab_stride;
     long long pages;
     int ring;
+    const float* sink;               // per query head, or null: a logit without key and value in the softmax's denominator
 };
 
 // One work item: a 128-query tile of one query head of one sequence, and the key tiles it takes.
@@ -636,7 +637,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 const float m = fmaxf(m_ref, other.x);
                 const float f_mine = m_ref == -INFINITY ? 0.f : ft_exp2(m_ref - m);
                 const float f_theirs = other.x == -INFINITY ? 0.f : ft_exp2(other.x - m);
-                float f = 1.f / (l_run * f_mine + other.y * f_theirs);
+                // a sink logit (natural units; the maxima are in log2 units) joins the denominator only
+                float f = 1.f / (l_run * f_mine + other.y * f_theirs +
+                                 (past.sink ? exp2f(past.sink[it.hq] * 1.4426950408889634f - m) : 0.f));
                 const long long tok = it.s0 + row_l;
                 if (gate) f *= sigmoid_f32(__bfloat162float(gate[tok * ldg + it.hq]));
                 bf16* dst = ctx + tok * ldc + (long long)it.hq * HD + g * HALF;
@@ -751,13 +754,13 @@ static int launch_ft(void* ctx, long long ldc, const void* q, const void* k, con
 // base and pitch.  err: device int that a block raises when one of its bounded waits runs out.
 extern "C" int cm_attn_prefill_tc(void* ctx, long long ldc, const void* q, const void* k, const void* v, long long ld,
                                   const void* gate, long long ldg, const int* seq_start, int B, int max_len,
-                                  long long T, int QH, int KVH, int HD, int window, float scale, int* err,
-                                  cudaStream_t st) {
+                                  long long T, int QH, int KVH, int HD, int window, float scale, const float* sink,
+                                  int* err, cudaStream_t st) {
     if (B <= 0 || max_len <= 0) return CM_OK;
     if (QH % KVH) CM_REFUSE("attn_prefill_tc: %d query heads over %d key heads", QH, KVH);
     if (ld % 8 || ldc % 8 || (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)ctx) & 15))
         CM_REFUSE("attn_prefill_tc: row pitches %lld, %lld must be multiples of 8 and the operands 16-byte aligned", ld, ldc);
-    const FtPast none = {nullptr, nullptr, nullptr, 0, 0, 0};
+    const FtPast none = {nullptr, nullptr, nullptr, 0, 0, 0, sink};
     if (HD == 64)
         return launch_ft<64, FT_STAGES_64, false>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, T, QH, KVH, window, scale,
                                        none, nullptr, err, st);
@@ -775,7 +778,7 @@ extern "C" int cm_attn_append_tc(void* ctx, long long ldc, const void* q, const 
                                  const void* gate, long long ldg, const int* seq_start, const int* seq_pos0,
                                  const int* seq_slot, const void* pool, long long pages, const int* ptab,
                                  long long ptab_stride, int ring, int B, int max_len, long long T, int QH, int KVH,
-                                 int HD, int window, float scale, int* err, cudaStream_t st) {
+                                 int HD, int window, float scale, const float* sink, int* err, cudaStream_t st) {
     if (B <= 0 || max_len <= 0) return CM_OK;
     if (QH % KVH) CM_REFUSE("attn_append_tc: %d query heads over %d key heads", QH, KVH);
     if (ring % PAGE_TOKENS) CM_REFUSE("attn_append_tc: ring of %d entries is no multiple of %d", ring, PAGE_TOKENS);
@@ -784,7 +787,7 @@ extern "C" int cm_attn_append_tc(void* ctx, long long ldc, const void* q, const 
     if (ld % 8 || ldc % 8 || (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)ctx | (uintptr_t)pool) & 15))
         CM_REFUSE("attn_append_tc: row pitches %lld, %lld must be multiples of 8 and the operands 16-byte aligned", ld, ldc);
     if (2 * pages * KVH * PAGE_TOKENS > 0x7fffffffLL) CM_REFUSE("attn_append_tc: a cache of %lld pages is too large", pages);
-    const FtPast past = {seq_pos0, seq_slot, ptab, ptab_stride, pages, ring};
+    const FtPast past = {seq_pos0, seq_slot, ptab, ptab_stride, pages, ring, sink};
     if (HD == 64)
         return launch_ft<64, FT_STAGES_64, true>(ctx, ldc, q, k, v, ld, gate, ldg, seq_start, B, max_len, T, QH, KVH, window, scale,
                                       past, pool, err, st);

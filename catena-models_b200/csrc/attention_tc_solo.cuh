@@ -376,7 +376,8 @@ attn_prefill_tc_solo_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             __syncwarp();
             if (lane == 0) mbar_arrive(o_free);                   // O may take the next item's first product
             if (row_l < it.len) {
-                float f = 1.f / l_run;
+                // a sink logit (natural units; m_ref is in log2 units) joins the denominator only
+                float f = 1.f / (l_run + (past.sink ? exp2f(past.sink[it.hq] * 1.4426950408889634f - m_ref) : 0.f));
                 const long long tok = it.s0 + row_l;
                 if (gate) f *= sigmoid_f32(__bfloat162float(gate[tok * ldg + it.hq]));
                 bf16* dst = ctx + tok * ldc + (long long)it.hq * HD;

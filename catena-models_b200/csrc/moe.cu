@@ -1,0 +1,262 @@
+// Routed feed-forward (mixture of experts) without a look from the host: a router kernel scores the
+// experts of every token and picks the best `top`; the (token, choice) pairs are put into the order of
+// their experts by counting (a list of row tiles, each of one expert, comes with it); two grouped
+// products then run the experts over their own rows only.  Everything a launch needs to know about the
+// routing it reads from device memory, so a step of given shape launches the same kernels with the same
+// arguments whatever the router decides, and can be recorded into a graph.
+//
+//   scores      s = gate(W_r h) in float (gate: sigmoid or softmax over the experts);
+//               the `top` largest, lowest index first among equals; weights = the chosen scores,
+//               optionally divided by their sum
+//   experts     a = act(W_gate x) * (W_up x), y = W_down a, with x = weight * h (the weight on the
+//               expert's INPUT) or x = h and y = weight * y (the weight on its output)
+//   result      one row of y per pair, float, pair p = token * top + choice: the consumer adds a token's
+//               rows in the order of the choices.
+//
+// A pair's result does not depend on which tile it lands in (every output is one dot product in a fixed
+// order), so the order of the pairs inside an expert, which comes from atomic counters, changes nothing.
+#include "common.cuh"
+#include <math.h>
+
+#define MOE_TM 32
+#define MOE_TN 64
+#define MOE_BK 16
+#define MOE_THREADS 256
+
+// ------------------------------------------------------------------------------ routing
+// One block per token.  ids[p] = expert of pair p (-1 for rows of padding), wts[p] its weight.
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_router_kernel(int* __restrict__ ids, float* __restrict__ wts, int* __restrict__ counts,
+                  const T* __restrict__ h, const T* __restrict__ wr, const int* __restrict__ tok_seq, int W, int E,
+                  int top, int softmax_gate, int renormalize) {
+    extern __shared__ float score[];              // [E]
+    pdl_trigger();
+    pdl_wait();
+    const long long t = blockIdx.x;
+    if (tok_seq && tok_seq[t] < 0) {
+        for (int j = threadIdx.x; j < top; j += blockDim.x) ids[t * top + j] = -1;
+        return;
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const T* hr = h + t * W;
+    for (int e = warp; e < E; e += 4) {
+        const T* w = wr + (long long)e * W;
+        float acc = 0.f;
+        for (int c = lane; c < W; c += 32) acc = fmaf(to_f32(w[c]), to_f32(hr[c]), acc);
+        acc = warp_sum(acc);
+        if (lane == 0) score[e] = acc;
+    }
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    if (softmax_gate) {
+        float mx = -INFINITY, den = 0.f;
+        for (int e = 0; e < E; ++e) mx = fmaxf(mx, score[e]);
+        for (int e = 0; e < E; ++e) den += expf(score[e] - mx);
+        for (int e = 0; e < E; ++e) score[e] = expf(score[e] - mx) / den;
+    } else {
+        for (int e = 0; e < E; ++e) score[e] = sigmoid_f32(score[e]);
+    }
+    float total = 0.f;
+    for (int j = 0; j < top; ++j) {
+        int best = 0;
+        float bv = -INFINITY;
+        for (int e = 0; e < E; ++e)
+            if (score[e] > bv) {
+                bv = score[e];
+                best = e;
+            }
+        ids[t * top + j] = best;
+        wts[t * top + j] = bv;
+        total += bv;
+        score[best] = -INFINITY;
+        atomicAdd(counts + best, 1);
+    }
+    if (renormalize)
+        for (int j = 0; j < top; ++j) wts[t * top + j] /= total;
+}
+
+// One block, one thread's walk over the experts: where each expert's rows begin, and the list of row
+// tiles.  plan: [0] number of tiles, then per tile (expert, first row, rows).  cursor[e] = offset[e].
+__global__ void moe_plan_kernel(const int* __restrict__ counts, int* __restrict__ cursor, int* __restrict__ plan, int E) {
+    pdl_trigger();
+    pdl_wait();
+    if (threadIdx.x != 0) return;
+    int off = 0, n = 0;
+    for (int e = 0; e < E; ++e) {
+        const int c = counts[e];
+        cursor[e] = off;
+        for (int r = 0; r < c; r += MOE_TM) {
+            plan[1 + 3 * n] = e;
+            plan[2 + 3 * n] = off + r;
+            plan[3 + 3 * n] = min(MOE_TM, c - r);
+            ++n;
+        }
+        off += c;
+    }
+    plan[0] = n;
+}
+
+__global__ void moe_scatter_kernel(int* __restrict__ perm, int* __restrict__ cursor, const int* __restrict__ ids, long long P) {
+    pdl_trigger();
+    pdl_wait();
+    const long long p = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (p >= P) return;
+    const int e = ids[p];
+    if (e >= 0) perm[atomicAdd(cursor + e, 1)] = (int)p;
+}
+
+// work: int32 scratch of E (counts) + E (cursor) + 1 + 3 * max_tiles (plan) entries; perm: P entries.
+extern "C" int cm_moe_route(int dt, int* ids, float* wts, int* perm, int* work, const void* h, const void* wr,
+                            const int* tok_seq, long long rows, int W, int E, int top, int softmax_gate,
+                            int renormalize, cudaStream_t st) {
+    if (rows <= 0) return CM_OK;
+    if (top < 1 || top > E) CM_REFUSE("moe_route: %d of %d experts", top, E);
+    if ((size_t)E * sizeof(float) > 48 * 1024) CM_REFUSE("moe_route: %d experts", E);
+    int *counts = work, *cursor = work + E, *plan = work + 2 * E;
+    if (cudaMemsetAsync(counts, 0, (size_t)E * sizeof(int), st) != cudaSuccess) {
+        cm_set_error("moe_route: memset failed");
+        return CM_ERR_LAUNCH;
+    }
+    const size_t smem = (size_t)E * sizeof(float);
+    if (dt == DT_F32)
+        cm_launch(moe_router_kernel<float>, (unsigned)rows, 128, smem, st, ids, wts, counts, (const float*)h, (const float*)wr,
+                  tok_seq, W, E, top, softmax_gate, renormalize);
+    else if (dt == DT_BF16)
+        cm_launch(moe_router_kernel<bf16>, (unsigned)rows, 128, smem, st, ids, wts, counts, (const bf16*)h, (const bf16*)wr,
+                  tok_seq, W, E, top, softmax_gate, renormalize);
+    else
+        return CM_ERR_DTYPE;
+    CM_CHECK_LAUNCH();
+    cm_launch(moe_plan_kernel, 1, 32, 0, st, counts, cursor, plan, E);
+    CM_CHECK_LAUNCH();
+    const long long P = rows * top;
+    cm_launch(moe_scatter_kernel, (unsigned)((P + 255) / 256), 256, 0, st, perm, cursor, ids, P);
+    CM_CHECK_LAUNCH();
+    return CM_OK;
+}
+
+extern "C" int cm_moe_max_tiles(long long pairs, int E) {
+    const long long full = (pairs + MOE_TM - 1) / MOE_TM;
+    return (int)(full + (pairs < E ? pairs : E));
+}
+
+// ------------------------------------------------------------------------------ grouped products
+// UP:   a[row] = act(Wg_e x) * (Wu_e x) for the sorted rows of a tile; x = h[token of the pair] (times the
+//       pair's weight when scale_input); w: [E][2 F][K] (gate rows, then up rows); out a: [P][F], sorted order.
+// DOWN: y[pair] = Wd_e a[row] (times the pair's weight when scale_output); w: [E][N][K]; out y: [P][N] float,
+//       by pair.
+// A block computes MOE_TM rows x MOE_TN columns; a thread 4 rows x 2 columns (and both halves for UP).
+template <typename T, bool UP>
+__global__ void __launch_bounds__(MOE_THREADS)
+moe_grouped_kernel(void* __restrict__ out, const T* __restrict__ x, const T* __restrict__ w,
+                   const int* __restrict__ plan, const int* __restrict__ perm, const float* __restrict__ wts,
+                   int top, int N, int K, int apply_weight, int gelu) {
+    __shared__ float xs[MOE_BK][MOE_TM + 1];
+    __shared__ float ws[UP ? 2 : 1][MOE_BK][MOE_TN + 1];
+    __shared__ int src_row[MOE_TM];
+    __shared__ float row_w[MOE_TM];
+    pdl_trigger();
+    pdl_wait();
+    const int tile = blockIdx.x;
+    if (tile >= plan[0]) return;
+    const int e = plan[1 + 3 * tile], row0 = plan[2 + 3 * tile], n_rows = plan[3 + 3 * tile];
+    const int n0 = blockIdx.y * MOE_TN;
+    const int tid = threadIdx.x;
+    if (tid < MOE_TM) {
+        const int p = tid < n_rows ? perm[row0 + tid] : -1;
+        src_row[tid] = p < 0 ? -1 : (UP ? p / top : row0 + tid);
+        row_w[tid] = p < 0 ? 0.f : wts[p];
+    }
+    __syncthreads();
+    const int tr = tid / 32, tc = tid % 32;          // rows tr * 4 .. + 3, columns tc * 2, tc * 2 + 1
+    float acc[UP ? 2 : 1][4][2];
+#pragma unroll
+    for (int h = 0; h < (UP ? 2 : 1); ++h)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[h][i][0] = acc[h][i][1] = 0.f;
+    const T* we = w + (long long)e * (UP ? 2 : 1) * N * K;
+    for (int k0 = 0; k0 < K; k0 += MOE_BK) {
+        for (int i = tid; i < MOE_TM * MOE_BK; i += MOE_THREADS) {
+            const int r = i / MOE_BK, kk = i % MOE_BK;
+            float v = 0.f;
+            if (src_row[r] >= 0 && k0 + kk < K) {
+                v = to_f32(x[(long long)src_row[r] * K + k0 + kk]);
+                if (UP && apply_weight) v = rounded<T>(v * row_w[r]);       // the expert's input as it would be stored
+            }
+            xs[kk][r] = v;
+        }
+        for (int i = tid; i < MOE_TN * MOE_BK; i += MOE_THREADS) {
+            const int c = i / MOE_BK, kk = i % MOE_BK;
+            const bool in = n0 + c < N && k0 + kk < K;
+            ws[0][kk][c] = in ? to_f32(we[(long long)(n0 + c) * K + k0 + kk]) : 0.f;
+            if (UP) ws[1][kk][c] = in ? to_f32(we[(long long)(N + n0 + c) * K + k0 + kk]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < MOE_BK; ++kk) {
+            float xv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) xv[i] = xs[kk][tr * 4 + i];
+#pragma unroll
+            for (int h = 0; h < (UP ? 2 : 1); ++h) {
+                const float w0 = ws[h][kk][tc * 2], w1 = ws[h][kk][tc * 2 + 1];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    acc[h][i][0] = fmaf(xv[i], w0, acc[h][i][0]);
+                    acc[h][i][1] = fmaf(xv[i], w1, acc[h][i][1]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = tr * 4 + i;
+        if (r >= n_rows) continue;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            const int n = n0 + tc * 2 + c;
+            if (n >= N) continue;
+            if (UP) {
+                const float g = acc[0][i][c], u = acc[1][i][c];
+                float act;
+                if (gelu) act = 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+                else act = g * sigmoid_f32(g);
+                reinterpret_cast<T*>(out)[(long long)(row0 + r) * N + n] = from_f32<T>(act * u);
+            } else {
+                const int p = perm[row0 + r];
+                float y = acc[0][i][c];
+                if (apply_weight) y *= row_w[r];
+                reinterpret_cast<float*>(out)[(long long)p * N + n] = y;
+            }
+        }
+    }
+}
+
+template <typename T>
+static int launch_grouped(bool up, void* out, const void* x, const void* w, const int* work, const int* perm,
+                          const float* wts, int E, int top, int max_tiles, int N, int K, int apply_weight, int gelu,
+                          cudaStream_t st) {
+    const int* plan = work + 2 * E;
+    dim3 grid(max_tiles, (N + MOE_TN - 1) / MOE_TN);
+    if (up)
+        cm_launch(moe_grouped_kernel<T, true>, grid, MOE_THREADS, 0, st, out, (const T*)x, (const T*)w, plan, perm, wts, top, N,
+                  K, apply_weight, gelu);
+    else
+        cm_launch(moe_grouped_kernel<T, false>, grid, MOE_THREADS, 0, st, out, (const T*)x, (const T*)w, plan, perm, wts, top, N,
+                  K, apply_weight, gelu);
+    CM_CHECK_LAUNCH();
+    return CM_OK;
+}
+
+// up != 0: the gated first product (N = the experts' inner width, K = the model's width);
+// up == 0: the second product (N = the model's width, K = the inner width), rows of float by pair.
+extern "C" int cm_moe_grouped(int dt, int up, void* out, const void* x, const void* w, const int* work,
+                              const int* perm, const float* wts, int E, int top, int max_tiles, int N, int K,
+                              int apply_weight, int gelu, cudaStream_t st) {
+    if (max_tiles <= 0) return CM_OK;
+    if (dt == DT_F32) return launch_grouped<float>(up != 0, out, x, w, work, perm, wts, E, top, max_tiles, N, K, apply_weight, gelu, st);
+    if (dt == DT_BF16) return launch_grouped<bf16>(up != 0, out, x, w, work, perm, wts, E, top, max_tiles, N, K, apply_weight, gelu, st);
+    return CM_ERR_DTYPE;
+}

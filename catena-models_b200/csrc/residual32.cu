@@ -1,0 +1,164 @@
+// Row-wise kernels for models whose residual stream is kept in float whatever the activation type:
+// a norm that reads float rows and writes activations, the residual sum of several terms fused with
+// the norm of whatever runs next, and the concatenation [x; x0] that a looped stack feeds to the
+// projection at the start of a pass.
+//
+// A row is held in shared memory between the two passes over it (sum of squares, then scaling), so the
+// width is bounded by shared memory only.  All sums are float and run in a fixed order.
+#include "common.cuh"
+
+#define R32_THREADS 256
+#define R32_MAX_TERMS 4
+
+// One term of a residual sum: rows of `per_row` consecutive pieces each (a routed feed-forward leaves
+// one piece per chosen expert), stored as float or as activations, times a constant.
+struct ResidualTerm {
+    const void* p;
+    float scale;
+    int per_row;
+    int is_f32;
+};
+struct ResidualTerms {
+    ResidualTerm t[R32_MAX_TERMS];
+    int n;
+};
+
+template <typename T>
+__device__ __forceinline__ float term_at(const ResidualTerm& t, long long i) {
+    return t.is_f32 ? reinterpret_cast<const float*>(t.p)[i] : to_f32(reinterpret_cast<const T*>(t.p)[i]);
+}
+
+// y = T((x * inv) * w), inv = 1 / sqrt(mean(x^2) + eps); x float.
+template <typename T>
+__global__ void __launch_bounds__(R32_THREADS)
+norm_f32in_kernel(T* __restrict__ y, const float* __restrict__ x, const float* __restrict__ w, int H, float eps) {
+    extern __shared__ float row[];
+    __shared__ float scratch[32];
+    pdl_trigger();
+    pdl_wait();
+    const float* xr = x + (long long)blockIdx.x * H;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < H; c += R32_THREADS) {
+        const float v = xr[c];
+        row[c] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.f / sqrtf(ss / (float)H + eps);
+    T* yr = y + (long long)blockIdx.x * H;
+    for (int c = threadIdx.x; c < H; c += R32_THREADS) yr[c] = from_f32<T>((row[c] * inv) * w[c]);
+}
+
+// h += sum_i scale_i * sum_j term_i[row * per_row_i + j] (+ bias);  n = T(norm(h) * w) when n is given.
+// The terms are added to each other first, in their order, and their sum to h: x + (mixer + feed-forward).
+template <typename T>
+__global__ void __launch_bounds__(R32_THREADS)
+residual_add_norm_kernel(float* __restrict__ h, T* __restrict__ n_out, ResidualTerms terms,
+                         const float* __restrict__ bias, const float* __restrict__ w, int H, float eps) {
+    extern __shared__ float row[];
+    __shared__ float scratch[32];
+    pdl_trigger();
+    pdl_wait();
+    const long long r = blockIdx.x;
+    float* hr = h + r * H;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < H; c += R32_THREADS) {
+        float add = 0.f;
+        for (int i = 0; i < terms.n; ++i) {
+            const ResidualTerm& t = terms.t[i];
+            float s = 0.f;
+            for (int j = 0; j < t.per_row; ++j) s += term_at<T>(t, (r * t.per_row + j) * H + c);
+            add += t.scale * s;
+        }
+        float v = hr[c] + add;
+        if (bias) v += bias[c];
+        hr[c] = v;
+        row[c] = v;
+        ss += v * v;
+    }
+    if (!n_out) return;
+    ss = block_sum(ss, scratch);
+    const float inv = 1.f / sqrtf(ss / (float)H + eps);
+    T* nr = n_out + r * H;
+    for (int c = threadIdx.x; c < H; c += R32_THREADS) nr[c] = from_f32<T>((row[c] * inv) * w[c]);
+}
+
+// out[r] = T([a[r]; b[r]]) for float rows a and b of width H: the input of a projection over both.
+template <typename T>
+__global__ void concat_cast_kernel(T* __restrict__ out, const float* __restrict__ a, const float* __restrict__ b,
+                                   long long rows, int H) {
+    pdl_trigger();
+    pdl_wait();
+    const long long total = rows * 2 * H;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / (2 * H);
+        const int c = (int)(i - r * 2 * H);
+        out[i] = from_f32<T>(c < H ? a[r * H + c] : b[r * H + c - H]);
+    }
+}
+
+static int row_smem(int H, size_t* out) {
+    *out = (size_t)H * sizeof(float);
+    if (*out > 200 * 1024) CM_REFUSE("a row of %d floats does not fit shared memory", H);
+    return CM_OK;
+}
+
+extern "C" int cm_norm_f32in(int dt, void* y, const float* x, const float* w, int rows, int H, float eps,
+                             cudaStream_t st) {
+    if (rows <= 0) return CM_OK;
+    size_t smem;
+    if (row_smem(H, &smem) != CM_OK) return CM_ERR_SHAPE;
+    if (dt == DT_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(norm_f32in_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cm_launch(norm_f32in_kernel<float>, rows, R32_THREADS, smem, st, (float*)y, x, w, H, eps);
+    } else if (dt == DT_BF16) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(norm_f32in_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cm_launch(norm_f32in_kernel<bf16>, rows, R32_THREADS, smem, st, (bf16*)y, x, w, H, eps);
+    } else
+        return CM_ERR_DTYPE;
+    CM_CHECK_LAUNCH();
+    return CM_OK;
+}
+
+// terms: n_terms entries of (pointer, scale, pieces per row, stored as float?) in four parallel arrays.
+extern "C" int cm_residual_add_norm(int dt, float* h, void* n_out, int n_terms, const void* const* term_ptr,
+                                    const float* term_scale, const int* term_per_row, const int* term_is_f32,
+                                    const float* bias, const float* w, int rows, int H, float eps, cudaStream_t st) {
+    if (rows <= 0) return CM_OK;
+    if (n_terms < 0 || n_terms > R32_MAX_TERMS) CM_REFUSE("residual_add_norm: %d terms (at most %d)", n_terms, R32_MAX_TERMS);
+    if (n_out && !w) CM_REFUSE("residual_add_norm: a norm needs its weight");
+    size_t smem;
+    if (row_smem(H, &smem) != CM_OK) return CM_ERR_SHAPE;
+    ResidualTerms terms;
+    terms.n = n_terms;
+    for (int i = 0; i < R32_MAX_TERMS; ++i) {
+        terms.t[i].p = i < n_terms ? term_ptr[i] : nullptr;
+        terms.t[i].scale = i < n_terms ? term_scale[i] : 0.f;
+        terms.t[i].per_row = i < n_terms ? term_per_row[i] : 0;
+        terms.t[i].is_f32 = i < n_terms ? term_is_f32[i] : 0;
+    }
+    if (dt == DT_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(residual_add_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cm_launch(residual_add_norm_kernel<float>, rows, R32_THREADS, smem, st, h, (float*)n_out, terms, bias, w, H, eps);
+    } else if (dt == DT_BF16) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(residual_add_norm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cm_launch(residual_add_norm_kernel<bf16>, rows, R32_THREADS, smem, st, h, (bf16*)n_out, terms, bias, w, H, eps);
+    } else
+        return CM_ERR_DTYPE;
+    CM_CHECK_LAUNCH();
+    return CM_OK;
+}
+
+extern "C" int cm_concat_cast(int dt, void* out, const float* a, const float* b, long long rows, int H, cudaStream_t st) {
+    if (rows <= 0) return CM_OK;
+    const long long total = rows * 2 * H;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    if (dt == DT_F32)
+        cm_launch(concat_cast_kernel<float>, blocks, 256, 0, st, (float*)out, a, b, rows, H);
+    else if (dt == DT_BF16)
+        cm_launch(concat_cast_kernel<bf16>, blocks, 256, 0, st, (bf16*)out, a, b, rows, H);
+    else
+        return CM_ERR_DTYPE;
+    CM_CHECK_LAUNCH();
+    return CM_OK;
+}

@@ -42,6 +42,8 @@ class ModelDefinition:
     embedding_scale: float = 1.0     # factor on every embedding row
     logit_scale: float = 1.0         # factor on the logits
     logit_softcap: float = 0.0       # logits <- cap * tanh(logits / cap) after the scale; 0: none
+    residual_float32: bool = False   # the residual stream is float32 whatever the activation dtype (the blocks must take it)
+    keep_embedding: bool = False     # a copy of the embedding rows stays in StepBatch.shared["embedding"] for the blocks
 
     def parts(self):
         out = list(self.blocks) + [self.final_norm]

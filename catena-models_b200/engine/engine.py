@@ -134,8 +134,9 @@ class Engine:
         # the distinct state specs of the model: what they say about a length picks the recording
         self._class_specs = []
         for spec in self.cache.state_specs:
-            if spec is not None and spec not in self._class_specs:
-                self._class_specs.append(spec)
+            for part in (getattr(spec, "parts", None) or (spec,)):     # a layer of several mixers: each one's spec
+                if part is not None and part not in self._class_specs:
+                    self._class_specs.append(part)
         self.steps_run = 0
         self.kernel_launches = 0
 

@@ -29,6 +29,7 @@ class DecoderModel:
         self.supports_append = all(part.all_support_append() for part in definition.parts())
         self.fusable_decode = all(part.all_fused_decode_ok() for part in definition.parts())
         self.token_error = rt.token_error
+        self.residual_dtype = torch.float32 if definition.residual_float32 else rt.dtype
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -36,6 +37,9 @@ class DecoderModel:
         from ..config.registry import config_from_folder
 
         arch, config = config_from_folder(folder)
+        if hasattr(config, "with_tensor_shapes"):          # sizes that the configuration leaves to the tensors
+            from ..weights.loader import tensor_shapes
+            config = config.with_tensor_shapes(tensor_shapes(folder))
         rt = Runtime(dtype, device)
         definition = arch.define(config)
         tensors = load_tensors(folder, definition.tensor_specs(), rt.device, widen=dtype == torch.float32)
@@ -47,6 +51,8 @@ class DecoderModel:
         from ..config.registry import config_from_dict
 
         arch, config = config_from_dict(config_dict)
+        if hasattr(config, "with_tensor_shapes"):
+            config = config.with_tensor_shapes({n: tuple(t.shape) for n, t in tensors.items()})
         rt = Runtime(dtype, device)
         definition = arch.define(config)
         bound = adopt_tensors(tensors, definition.tensor_specs(), rt.device, widen=dtype == torch.float32)
@@ -92,9 +98,12 @@ class DecoderModel:
         batch.shared.clear()
         if batch.layout.U:
             kernels.scatter_i32(cache.ptab_all, batch.upd_index, batch.upd_value, batch.upd_count, batch.layout.U)
-        h = torch.empty((batch.T, self.hidden_size), dtype=rt.dtype, device=rt.device)
+        # the residual stream: in the activation dtype, or in float for a definition that says so
+        h = torch.empty((batch.T, self.hidden_size), dtype=self.residual_dtype, device=rt.device)
         kernels.embed_gather(h, self.embedding, batch.tokens, self.token_error, sampled=batch.prev_sampled,
                              scale=self.definition.embedding_scale)
+        if self.definition.keep_embedding:
+            batch.shared["embedding"] = h.clone()          # blocks add to h in place; some read the embedding again
         plan = self.plan
         first_norm = self.blocks[plan[0].block].input_norm
         n = first_norm.apply(rt, h) if first_norm is not None else None
@@ -116,7 +125,7 @@ class DecoderModel:
         if whole and n is not None:
             logits = rt.linear(n, self.head_weight, out_dtype=torch.float32)
         else:
-            rows = torch.empty((batch.n_want, self.hidden_size), dtype=rt.dtype, device=rt.device)
+            rows = torch.empty((batch.n_want, self.hidden_size), dtype=h.dtype, device=rt.device)
             kernels.gather_rows(rows, h, batch.want_rows)
             normed = self.final_norm.apply(rt, rows)
             logits = rt.linear(normed, self.head_weight, out_dtype=torch.float32)

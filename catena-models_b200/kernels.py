@@ -33,26 +33,35 @@ _SIGNATURES = {
     "cm_gemm_tc": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _vp, _vp],
     "cm_gemm_tc_few_rows": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _vp, _vp],
     "cm_qk_prepare": [_i, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _i,
-                      _i, _f, _i, _vp],
-    "cm_attn_prefill_simt": [_i, _vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
-    "cm_attn_prefill_mma": [_vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
-    "cm_attn_prefill_tc": [_vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _i, _i, _ll, _i, _i, _i, _i, _f, _vp, _vp],
+                      _i, _f, _i, _f, _i, _vp],
+    "cm_attn_prefill_simt": [_i, _vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _vp],
+    "cm_attn_prefill_mma": [_vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _vp],
+    "cm_attn_prefill_tc": [_vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _i, _i, _ll, _i, _i, _i, _i, _f, _vp, _vp, _vp],
     "cm_attn_decode": [_i, _vp, _ll, _vp, _ll, _vp, _ll, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _i, _i, _i,
-                       _i, _f, _vp, _vp, _vp],
+                       _i, _f, _vp, _vp, _vp, _vp],
     "cm_gemm_skinny_shortconv": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _ll, _vp],
     "cm_shortconv": [_i, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "cm_attn_append_simt": [_i, _vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _vp, _vp, _vp, _ll, _vp, _ll, _i, _i, _i, _i,
-                            _i, _i, _i, _f, _vp],
+                            _i, _i, _i, _f, _vp, _vp],
     "cm_attn_append_mma": [_vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _vp, _vp, _vp, _ll, _vp, _ll, _i, _i, _i, _i, _i,
-                           _i, _i, _f, _vp],
+                           _i, _i, _f, _vp, _vp],
     "cm_attn_append_tc": [_vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _vp, _vp, _vp, _ll, _vp, _ll, _i, _i, _i, _ll, _i,
-                          _i, _i, _i, _f, _vp, _vp],
+                          _i, _i, _i, _f, _vp, _vp, _vp],
     "cm_gemm_tc_parts": [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _i, _i, _vp, _vp],
     "cm_kv_store": [_i, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _ll, _i, _i, _i, _i, _vp],
     "cm_sample": [_vp, _vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp],
     "cm_scatter_i32": [_vp, _vp, _vp, _vp, _i, _vp],
     "cm_zero_slots": [_vp, _i, _ll, _ll, ctypes.POINTER(ctypes.c_int), _i, _vp],
     "cm_copy_pages": [_vp, _vp, _vp, _i, _i, _ll, _ll, _vp],
+    "cm_norm_f32in": [_i, _vp, _vp, _vp, _i, _i, _f, _vp],
+    "cm_residual_add_norm": [_i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp],
+    "cm_concat_cast": [_i, _vp, _vp, _vp, _ll, _i, _vp],
+    "cm_shift_mix": [_i, _vp, _vp, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _i, _ll, _i, _vp],
+    "cm_lowrank_decay": [_i, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _vp],
+    "cm_capped_gates": [_i, _vp, _vp, _vp, _vp, _f, _ll, _i, _i, _vp],
+    "cm_matrix_scan": [_i, _i, _vp, _i, _vp],
+    "cm_moe_route": [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _vp],
+    "cm_moe_grouped": [_i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
 }
 
 
@@ -333,6 +342,11 @@ class PartialSums:
         return self.parts.shape[1:]
 
 
+class Terms(list):
+    """What a sublayer adds to a float32 residual stream: (tensor, factor, pieces per row) entries; the
+    tensor holds rows * pieces rows, float32 or in the activation dtype (`residual_add_norm`)."""
+
+
 def add_norm(h_out, n_out, m, h_in, w_post, w_next, eps_post, eps_next):
     """h_out = h_in + (norm(m; w_post) or m); n_out = norm(h_out; w_next) when w_next is given.
     m: a tensor, or the PartialSums a product left."""
@@ -512,42 +526,46 @@ def gemm_tc_few_rows(y, x, w, swiglu=False, err=None, splits=0):
 
 # -------------------------------------------------------------------------- attention
 def qk_prepare(qkv, wq, wk, rate, tok_pos, tok_seq, seq_slot, seq_end, pool, pages, ptab, ring,
-               QH, KVH, HD, eps, interleaved=False):
+               QH, KVH, HD, eps, interleaved=False, q_temp=None):
     """Head norm + rotation in place on the q and k columns of qkv; k and v go to the cache
     (pool: this layer's [2, pages, KVH, 64, HD] storage, or None to write no cache).  The rotation
-    pairs element i with i + HD/2, or, with `interleaved`, 2i with 2i + 1."""
+    pairs element i with i + HD/2, or, with `interleaved`, 2i with 2i + 1.  `q_temp` = (coef, every):
+    the queries at position p are multiplied by 1 + coef * ln(floor((p + 1) / every) + 1)."""
+    qt_coef, qt_every = (float(q_temp[0]), int(q_temp[1])) if q_temp else (0.0, 0)
     T = qkv.shape[0]
     _check(lib().cm_qk_prepare(dtype_code(qkv.dtype), _ptr(qkv), qkv.stride(0), _ptr(wq), _ptr(wk), _ptr(rate),
                                _ptr(tok_pos), _ptr(tok_seq), _ptr(seq_slot), _ptr(seq_end), _ptr(pool), pages,
                                _ptr(ptab), 0 if ptab is None else ptab.stride(0), ring, T, QH, KVH, HD, eps,
-                               int(interleaved), _stream()), "qk_prepare",
+                               int(interleaved), qt_coef, qt_every, _stream()), "qk_prepare",
            cost=lambda: (f"{T} tokens, {QH}+{KVH} heads of {HD}",
                          T * HD * qkv.element_size() * (2 * QH + (2 * KVH if pool is None else 4 * KVH)), 0))
 
 
-def attn_prefill_simt(ctx, q, k, v, gate, seq_start, B, max_len, QH, KVH, HD, window, scale):
-    """q, k, v, gate are column views of one packed row-major buffer (same row stride)."""
+def attn_prefill_simt(ctx, q, k, v, gate, seq_start, B, max_len, QH, KVH, HD, window, scale, sink=None):
+    """q, k, v, gate are column views of one packed row-major buffer (same row stride).  `sink` (all
+    attention kernels): float32 [QH], a learned logit per query head that joins the softmax's denominator
+    and nothing else (it has no key and no value), or None."""
     if not (q.stride(0) == k.stride(0) == v.stride(0)):
         raise KernelError("attn_prefill: q, k and v must share a row stride")
     _check(lib().cm_attn_prefill_simt(dtype_code(q.dtype), _ptr(ctx), ctx.stride(0), _ptr(q), _ptr(k), _ptr(v),
                                       q.stride(0), _ptr(gate), 0 if gate is None else gate.stride(0),
-                                      _ptr(seq_start), B, max_len, QH, KVH, HD, window, scale, _stream()),
+                                      _ptr(seq_start), B, max_len, QH, KVH, HD, window, scale, _ptr(sink), _stream()),
            "attn_prefill_simt",
            cost=lambda: (f"{B} sequences up to {max_len}, {QH}/{KVH} heads of {HD}, window {window}", 0, 0))
 
 
-def attn_prefill_mma(ctx, q, k, v, gate, seq_start, B, max_len, QH, KVH, HD, window, scale):
+def attn_prefill_mma(ctx, q, k, v, gate, seq_start, B, max_len, QH, KVH, HD, window, scale, sink=None):
     """The same on the tensor cores: bfloat16, head sizes that are multiples of 16 up to 128."""
     if not (q.stride(0) == k.stride(0) == v.stride(0)) or q.dtype != torch.bfloat16:
         raise KernelError("attn_prefill_mma: bfloat16 q, k and v that share a row stride")
     _check(lib().cm_attn_prefill_mma(_ptr(ctx), ctx.stride(0), _ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(gate),
                                      0 if gate is None else gate.stride(0), _ptr(seq_start), B, max_len, QH, KVH,
-                                     HD, window, scale, _stream()), "attn_prefill_mma",
+                                     HD, window, scale, _ptr(sink), _stream()), "attn_prefill_mma",
            cost=lambda: (f"{B} sequences up to {max_len}, {QH}/{KVH} heads of {HD}, window {window}", 0, 0))
 
 
 def attn_append(ctx, q, k, v, gate, seq_start, seq_pos0, seq_slot, pool, pages, ptab, ring, B, max_len, QH, KVH, HD,
-                window, scale, tensor_cores=True):
+                window, scale, tensor_cores=True, sink=None):
     """Attention of a step whose sequences may stand at seq_pos0[b] > 0: keys and values below that
     position come from the paged cache `pool`, the rest from the step's own rows (q, k, v as for the
     prefill kernels), which the caller writes to the cache afterwards (`kv_store`).  bfloat16 with a
@@ -558,7 +576,7 @@ def attn_append(ctx, q, k, v, gate, seq_start, seq_pos0, seq_slot, pool, pages, 
            and (q.data_ptr() | k.data_ptr() | v.data_ptr() | pool.data_ptr()) % 16 == 0)
     common = (_ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(gate), 0 if gate is None else gate.stride(0), _ptr(seq_start),
               _ptr(seq_pos0), _ptr(seq_slot), _ptr(pool), pages, _ptr(ptab), ptab.stride(0), ring, B, max_len, QH, KVH,
-              HD, window, scale, _stream())
+              HD, window, scale, _ptr(sink), _stream())
     if mma:
         _check(lib().cm_attn_append_mma(_ptr(ctx), ctx.stride(0), *common), "attn_append_mma")
     else:
@@ -566,7 +584,7 @@ def attn_append(ctx, q, k, v, gate, seq_start, seq_pos0, seq_slot, pool, pages, 
 
 
 def attn_append_tc(ctx, q, k, v, gate, seq_start, seq_pos0, seq_slot, pool, pages, ptab, ring, B, max_len, QH, KVH, HD,
-                   window, scale, err=None):
+                   window, scale, err=None, sink=None):
     """`attn_append` on the tcgen05 tensor cores: bfloat16, head size 64 or 128, the cache read page by
     page with TMA.  err: device int32 that a block raises if a bounded pipeline wait runs out."""
     if (not (q.stride(0) == k.stride(0) == v.stride(0)) or q.dtype != torch.bfloat16 or pool.dtype != torch.bfloat16
@@ -577,7 +595,7 @@ def attn_append_tc(ctx, q, k, v, gate, seq_start, seq_pos0, seq_slot, pool, page
     _check(lib().cm_attn_append_tc(_ptr(ctx), ctx.stride(0), _ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(gate),
                                    0 if gate is None else gate.stride(0), _ptr(seq_start), _ptr(seq_pos0),
                                    _ptr(seq_slot), _ptr(pool), pages, _ptr(ptab), ptab.stride(0), ring, B, max_len,
-                                   q.shape[0], QH, KVH, HD, window, scale, _ptr(err), _stream()), "attn_append_tc",
+                                   q.shape[0], QH, KVH, HD, window, scale, _ptr(sink), _ptr(err), _stream()), "attn_append_tc",
            cost=lambda: (f"{B} sequences of up to {max_len} rows, {QH}/{KVH} heads of {HD}, window {window}", 0, 0))
 
 
@@ -590,7 +608,7 @@ def kv_store(kv, tok_pos, tok_seq, seq_slot, seq_end, pool, pages, ptab, ring, K
            "kv_store")
 
 
-def attn_prefill_tc(ctx, q, k, v, gate, seq_start, B, max_len, QH, KVH, HD, window, scale, err=None):
+def attn_prefill_tc(ctx, q, k, v, gate, seq_start, B, max_len, QH, KVH, HD, window, scale, err=None, sink=None):
     """The same on the tcgen05 tensor cores (TMA-fed, scores and outputs in tensor memory): bfloat16,
     head size 64 or 128.  q, k and v are column blocks of one row-major buffer.  err: device int32
     that a block raises if one of its bounded pipeline waits runs out."""
@@ -598,7 +616,7 @@ def attn_prefill_tc(ctx, q, k, v, gate, seq_start, B, max_len, QH, KVH, HD, wind
         raise KernelError("attn_prefill_tc: bfloat16 q, k and v that share rows and a row stride")
     _check(lib().cm_attn_prefill_tc(_ptr(ctx), ctx.stride(0), _ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(gate),
                                     0 if gate is None else gate.stride(0), _ptr(seq_start), B, max_len, q.shape[0],
-                                    QH, KVH, HD, window, scale, _ptr(err), _stream()), "attn_prefill_tc",
+                                    QH, KVH, HD, window, scale, _ptr(sink), _ptr(err), _stream()), "attn_prefill_tc",
            cost=lambda: (f"{B} sequences up to {max_len}, {QH}/{KVH} heads of {HD}, window {window}", 0, 0))
 
 
@@ -622,12 +640,12 @@ def attn_decode_scratch(B, QH, HD, n_chunks, device):
 
 
 def attn_decode(ctx, q, gate, seq_pos, seq_slot, pool, pages, ptab, ring, window, QH, KVH, HD, n_chunks,
-                scale, part_o, part_ml):
+                scale, part_o, part_ml, sink=None):
     B = q.shape[0]
     _check(lib().cm_attn_decode(dtype_code(q.dtype), _ptr(ctx), ctx.stride(0), _ptr(q), q.stride(0), _ptr(gate),
                                 0 if gate is None else gate.stride(0), _ptr(seq_pos), _ptr(seq_slot), _ptr(pool),
                                 pages, _ptr(ptab), ptab.stride(0), ring, window, B, QH, KVH, HD, n_chunks, scale,
-                                _ptr(part_o), _ptr(part_ml), _stream()), "attn_decode", 2,
+                                _ptr(part_o), _ptr(part_ml), _ptr(sink), _stream()), "attn_decode", 2,
            cost=lambda: (f"{B} sequences, {QH}/{KVH} heads of {HD}, window {window}, {n_chunks} chunks", 0, 0))
 
 
@@ -706,3 +724,143 @@ def zero_slots(store, slots):
     ids = (ctypes.c_int * len(slots))(*slots)
     n_launches = -(-len(slots) // 64)
     _check(lib().cm_zero_slots(_ptr(store), layers, total, row_bytes, ids, len(slots), _stream()), "zero_slots", n_launches)
+
+
+# ------------------------------------------------------------------ float residual stream
+def norm_f32in(out, x, w, eps):
+    """out = norm(x) * w for float32 rows x; out in the activation dtype."""
+    _need_cuda(out, x, w)
+    rows, H = x.shape
+    if x.dtype != torch.float32 or not x.is_contiguous() or not out.is_contiguous():
+        raise KernelError("norm_f32in takes contiguous float32 rows")
+    _check(lib().cm_norm_f32in(dtype_code(out.dtype), _ptr(out), _ptr(x), _ptr(w), rows, H, eps, _stream()), "norm_f32in",
+           cost=lambda: (f"{rows}x{H}", _nbytes(x, out, w), 4 * rows * H))
+
+
+def residual_add_norm(h, terms, n_out=None, w_next=None, eps=0.0, bias=None):
+    """h (float32, in place) += sum over `terms` of scale * (the sum of a row's pieces) (+ bias, a float32
+    row); n_out = norm(h) * w_next in the activation dtype when given.  A term is (tensor, scale, pieces
+    per row): the tensor holds rows * pieces rows of h's width, float32 or the activation dtype."""
+    rows, H = h.shape
+    if h.dtype != torch.float32 or not h.is_contiguous() or len(terms) > 4:
+        raise KernelError("residual_add_norm: a contiguous float32 stream and at most four terms")
+    act = n_out.dtype if n_out is not None else next((t.dtype for t, _, _ in terms if t.dtype != torch.float32), torch.float32)
+    for t, _, per_row in terms:
+        if not t.is_contiguous() or t.numel() != rows * per_row * H or t.dtype not in (torch.float32, act):
+            raise KernelError("residual_add_norm: a term's shape or dtype does not fit")
+    n = len(terms)
+    ptrs = (ctypes.c_void_p * 4)(*[t.data_ptr() for t, _, _ in terms], *([None] * (4 - n)))
+    scales = (ctypes.c_float * 4)(*[float(s) for _, s, _ in terms], *([0.0] * (4 - n)))
+    per = (ctypes.c_int * 4)(*[int(p) for _, _, p in terms], *([0] * (4 - n)))
+    f32 = (ctypes.c_int * 4)(*[int(t.dtype == torch.float32) for t, _, _ in terms], *([0] * (4 - n)))
+    _check(lib().cm_residual_add_norm(dtype_code(act), _ptr(h), _ptr(n_out), n, ptrs, scales, per, f32, _ptr(bias),
+                                      _ptr(w_next), rows, H, eps, _stream()), "residual_add_norm",
+           cost=lambda: (f"{rows}x{H}, {n} terms", 2 * _nbytes(h) + _nbytes(n_out, *[t for t, _, _ in terms]), (n + 5) * rows * H))
+
+
+def concat_cast(out, a, b):
+    """out[r] = [a[r]; b[r]] in out's dtype, for float32 rows a and b."""
+    rows, H = a.shape
+    _check(lib().cm_concat_cast(dtype_code(out.dtype), _ptr(out), _ptr(a), _ptr(b), rows, H, _stream()), "concat_cast",
+           cost=lambda: (f"{rows}x{2 * H}", _nbytes(a, b, out), 0))
+
+
+# ------------------------------------------------------------------ mixers with a matrix state
+def shift_mix(out, h, mu, state, tok_seq, tok_pos, seq_pos0, seq_slot):
+    """out[s][t] = h[t] + (previous input - h[t]) * mu[s]; the previous input of a sequence's first row of
+    the step is the head of its state row (state: float32 [slots, n], n >= width)."""
+    S, rows, W = out.shape
+    _check(lib().cm_shift_mix(dtype_code(h.dtype), _ptr(out), _ptr(h), _ptr(mu), _ptr(state), state.stride(0),
+                              _ptr(tok_seq), _ptr(tok_pos), _ptr(seq_pos0), _ptr(seq_slot), S, rows, W, _stream()),
+           "shift_mix", cost=lambda: (f"{S}x{rows}x{W}", _nbytes(h, out, mu), 2 * S * rows * W))
+
+
+def lowrank_decay(out, x, w1, w2, w0):
+    """out = exp(-exp(W2 tanh(W1 x) + w0)) in float32: x [rows, W], W1 [R, W], W2 [C, R], w0 [C]."""
+    rows, W = x.shape
+    R, C = w1.shape[0], w2.shape[0]
+    if w1.dtype != x.dtype or w2.dtype != x.dtype or not (x.is_contiguous() and w1.is_contiguous() and w2.is_contiguous()):
+        raise KernelError("lowrank_decay: contiguous operands of one dtype")
+    _check(lib().cm_lowrank_decay(dtype_code(x.dtype), _ptr(out), _ptr(x), _ptr(w1), _ptr(w2), _ptr(w0), rows, W, R, C,
+                                  _stream()), "lowrank_decay",
+           cost=lambda: (f"{rows}x{W} rank {R} -> {C}", _nbytes(x, out, w1, w2), 2 * rows * R * (W + C)))
+
+
+def capped_gates(out, x, w, bias, cap):
+    """out[t] = [cap tanh(z / cap) for the first H rows of w; log sigmoid of the same for the other H],
+    z = w x + bias; out float32 [rows, 2 H]."""
+    rows, W = x.shape
+    H = w.shape[0] // 2
+    if w.dtype != x.dtype or not (x.is_contiguous() and w.is_contiguous()):
+        raise KernelError("capped_gates: contiguous operands of one dtype")
+    _check(lib().cm_capped_gates(dtype_code(x.dtype), _ptr(out), _ptr(x), _ptr(w), _ptr(bias), cap, rows, W, H, _stream()),
+           "capped_gates", cost=lambda: (f"{rows}x{W} -> {2 * H}", _nbytes(x, out, w), 4 * rows * H * W))
+
+
+class _ScanArgs(ctypes.Structure):
+    """csrc/recurrent.cu: ScanArgs."""
+    _fields_ = [("q", _vp), ("k", _vp), ("v", _vp), ("g", _vp), ("ldq", _ll), ("ldk", _ll), ("ldv", _ll), ("ldg", _ll),
+                ("decay", _vp), ("bonus", _vp), ("norm_w", _vp), ("out", _vp), ("ldo", _ll), ("state", _vp),
+                ("state_stride", _ll), ("state_offset", _ll), ("shift_src", _vp), ("W", _i), ("seq_start", _vp),
+                ("seq_slot", _vp), ("H", _i), ("D", _i), ("DV", _i), ("KS", _i), ("q_scale", _f), ("eps", _f)]
+
+
+def matrix_scan(mode, out, q, k, v, g, decay, bonus, norm_w, state, state_offset, seq_start, seq_slot, B, H, D, DV,
+                q_scale, eps, shift_src=None):
+    """The recurrence of a mixer with a matrix state per head over the step's rows of B sequences, with the
+    heads' unit norm, channel weights and output gate.  mode "decay": o = (S + diag(bonus) k v^T)^T q, then
+    S <- diag(decay_t) S + k v^T (decay float32 [rows, H D]; gate silu(g)).  mode "memory": log-domain
+    gates with a running maximum and a normaliser (decay float32 [rows, 2 H]: i, then f; gate sigmoid(g)).
+    q, k [rows, H D], v, g, out [rows, H DV]: activation dtype, any row pitch.  state: float32 [slots, n];
+    this mixer's part of a row starts at `state_offset`.  `shift_src` [rows, W] (mode "decay"): its last
+    row of each sequence is kept at the head of the state row."""
+    for t in (q, k, v, g, out):
+        if t.stride(1) != 1 or t.dtype != out.dtype:
+            raise KernelError("matrix_scan: row-major operands of one dtype")
+    a = _ScanArgs(q=_ptr(q), k=_ptr(k), v=_ptr(v), g=_ptr(g), ldq=q.stride(0), ldk=k.stride(0), ldv=v.stride(0),
+                  ldg=g.stride(0), decay=_ptr(decay), bonus=_ptr(bonus), norm_w=_ptr(norm_w), out=_ptr(out),
+                  ldo=out.stride(0), state=_ptr(state), state_stride=state.stride(0), state_offset=state_offset,
+                  shift_src=_ptr(shift_src), W=0 if shift_src is None else shift_src.shape[1], seq_start=_ptr(seq_start),
+                  seq_slot=_ptr(seq_slot), H=H, D=D, DV=DV, KS=0, q_scale=q_scale, eps=eps)
+    rows = q.shape[0]
+    _check(lib().cm_matrix_scan(dtype_code(out.dtype), {"decay": 0, "memory": 1}[mode], ctypes.byref(a), B, _stream()),
+           "matrix_scan_" + mode,
+           cost=lambda: (f"{B} sequences, {rows} rows, {H} heads of {D}x{DV}",
+                         _nbytes(q, k, v, g, out) + (0 if decay is None else rows * decay.shape[1] * 4) + 2 * B * H * D * DV * 4,
+                         6 * rows * H * D * DV))
+
+
+# ------------------------------------------------------------------ routed feed-forward
+def moe_max_tiles(pairs, experts):
+    fn = lib().cm_moe_max_tiles
+    fn.argtypes, fn.restype = [_ll, _i], _i
+    return fn(pairs, experts)
+
+
+def moe_route(ids, wts, perm, work, h, w_router, tok_seq, top, softmax_gate=False, renormalize=False):
+    """Scores of every token's experts in float32 (sigmoid, or softmax over the experts), the `top` best
+    (ids, wts: [rows * top]; -1 for rows of padding), and the pairs in the order of their experts (perm)
+    with the list of row tiles in `work` (int32, 2 E + 1 + 3 * moe_max_tiles entries)."""
+    rows, W = h.shape
+    E = w_router.shape[0]
+    if w_router.dtype != h.dtype or not (h.is_contiguous() and w_router.is_contiguous()):
+        raise KernelError("moe_route: contiguous operands of one dtype")
+    _check(lib().cm_moe_route(dtype_code(h.dtype), _ptr(ids), _ptr(wts), _ptr(perm), _ptr(work), _ptr(h), _ptr(w_router),
+                              _ptr(tok_seq), rows, W, E, top, int(softmax_gate), int(renormalize), _stream()), "moe_route", 3,
+           cost=lambda: (f"{rows}x{W} over {E}, top {top}", _nbytes(h, w_router), 2 * rows * E * W))
+
+
+def moe_grouped(out, x, w, work, perm, wts, top, max_tiles, up, apply_weight, gelu=False):
+    """The experts' products over the rows that `moe_route` gave them.  up: out[sorted row] = act(Wg x) * (Wu x)
+    with x = h[token] (times the pair's weight if apply_weight), w [E, 2 F, K]; else out[pair] (float32) = Wd a
+    (times the weight if apply_weight), w [E, N, K]."""
+    E = w.shape[0]
+    N = w.shape[1] // 2 if up else w.shape[1]
+    K = w.shape[2]
+    if w.dtype != x.dtype or not (x.is_contiguous() and w.is_contiguous() and out.is_contiguous()) or x.shape[1] != K:
+        raise KernelError("moe_grouped: contiguous operands of one dtype")
+    _check(lib().cm_moe_grouped(dtype_code(x.dtype), int(up), _ptr(out), _ptr(x), _ptr(w), _ptr(work), _ptr(perm), _ptr(wts),
+                                E, top, max_tiles, N, K, int(apply_weight), int(gelu), _stream()),
+           "moe_grouped_" + ("up" if up else "down"),
+           cost=lambda: (f"{out.shape[0]} rows, {w.shape[1]}x{K} per expert", _nbytes(x, out) + min(E, out.shape[0]) * w[0].numel() * w.element_size(),
+                         2 * out.shape[0] * w.shape[1] * K))

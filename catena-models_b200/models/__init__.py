@@ -1,2 +1,2 @@
 """Architectures.  Importing this package registers them by name."""
-from . import lfm3  # noqa: F401
+from . import lfm3, narasun  # noqa: F401

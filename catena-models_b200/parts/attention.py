@@ -14,6 +14,14 @@ top of started sequences) reads the keys below each sequence's first new positio
 and the rest from the step, and writes the step's keys and values to the cache afterwards, so
 that a ring still holds what the step's windows reach back to.  All sizes and switches are
 constructor parameters; the part knows neither its layer index nor its model.
+
+Further switches, all off by default: `scale` (the factor on q . k instead of 1/sqrt(head_dim)); `sink_name`
+(a learned logit per query head that joins the softmax's denominator and has neither key nor value);
+`q_temp` = (coef, every), a factor 1 + coef * ln(floor((p + 1) / every) + 1) on the queries at position p;
+`value_dim`, the size of a value head when it differs from the size of a query or key head.  The kernels
+and the cache work with one head size, so heads of unequal or odd sizes are padded with zero rows of the
+projections up to a common multiple of 16 (zero channels change no score and give zero outputs, which meet
+zero columns of the output projection); `out_dtype` = "float32" leaves the output projection's result in float.
 """
 from __future__ import annotations
 
@@ -34,9 +42,22 @@ class GQAttention(Mixer):
     supports_append = True
 
     def __init__(self, prefix, hidden, heads, kv_heads, head_dim, window, position, qk_norm_eps,
-                 output_gate, names=None, shares_kv=False):
+                 output_gate, names=None, shares_kv=False, scale=None, sink_name=None, q_temp=None, value_dim=None,
+                 out_dtype=None):
         names = names or {}
         n = lambda key, default: prefix + names.get(key, default)
+        qk_dim, v_dim = head_dim, value_dim or head_dim
+        if v_dim != qk_dim or (scale is not None and qk_dim % 16):
+            head_dim = -(-max(qk_dim, v_dim) // 16) * 16       # one padded head size for q, k and v
+            if qk_norm_eps is not None and head_dim != qk_dim:
+                raise ValueError("a head norm over padded heads is not built")
+        pad_qk = (heads, qk_dim, head_dim) if head_dim != qk_dim else None
+        pad_k = (kv_heads, qk_dim, head_dim) if head_dim != qk_dim else None
+        pad_v = (kv_heads, v_dim, head_dim) if head_dim != v_dim else None
+        self.qk_dim, self.v_dim = qk_dim, v_dim
+        self.sink_name, self.sink = (prefix + sink_name if sink_name else None), None
+        self.q_temp = (float(q_temp[0]), int(q_temp[1])) if q_temp else None
+        self.out_dtype = {None: None, "float32": torch.float32}[out_dtype]
         self.hidden, self.heads, self.kv_heads, self.head_dim = hidden, heads, kv_heads, head_dim
         self.window = int(window or 0)
         self.position = position
@@ -46,35 +67,45 @@ class GQAttention(Mixer):
         # shares_kv: this layer has no key/value projections of its own; it attends over the keys
         # and values of the layer that owns the state unit the plan gives it
         self.shares_kv = bool(shares_kv)
-        mats, rows = [n("q", "attn_q.weight")], [self.q_size]
+        mats, rows, pads = [n("q", "attn_q.weight")], [heads * qk_dim], [pad_qk]
         if not self.shares_kv:
             mats += [n("k", "attn_k.weight"), n("v", "attn_v.weight")]
-            rows += [self.kv_size, self.kv_size]
+            rows += [kv_heads * qk_dim, kv_heads * v_dim]
+            pads += [pad_k, pad_v]
         if self.output_gate:
             mats.append(n("gate", "attn_gate.weight"))
             rows.append(heads)
-        self.qkvg = Linear(mats, rows, hidden)
-        self.out = Linear(n("out", "attn_output.weight"), hidden, self.q_size)
+            pads.append(None)
+        self.qkvg = Linear(mats, rows, hidden, head_rows=pads)
+        self.out = Linear(n("out", "attn_output.weight"), hidden, heads * v_dim,
+                          head_cols=(heads, v_dim, head_dim) if head_dim != v_dim else None)
         self.q_norm_name, self.k_norm_name = n("q_norm", "attn_q_norm.weight"), n("k_norm", "attn_k_norm.weight")
         self.q_norm_w = self.k_norm_w = None
         # 1/sqrt(head_dim) in float32, as the reference bakes it (src/catena/qwen35_wmma_attention.hex:3-22)
-        self.scale = float(torch.tensor(1.0, dtype=torch.float32) / torch.sqrt(torch.tensor(float(head_dim), dtype=torch.float32)))
+        self.scale = float(torch.tensor(1.0, dtype=torch.float32) / torch.sqrt(torch.tensor(float(qk_dim), dtype=torch.float32)))
+        if scale is not None:
+            self.scale = float(scale)
 
     def children(self):
         return [self.qkvg, self.out, self.position]
 
     def tensor_specs(self):
+        specs = [TensorSpec(self.sink_name, (self.heads,), "vector")] if self.sink_name else []
         if self.qk_norm_eps is None:
-            return []
-        specs = [TensorSpec(self.q_norm_name, (self.head_dim,), "norm")]
+            return specs
+        specs.append(TensorSpec(self.q_norm_name, (self.head_dim,), "norm"))
         if not self.shares_kv:
             specs.append(TensorSpec(self.k_norm_name, (self.head_dim,), "norm"))
         return specs
 
     def bind(self, tensors, rt):
+        self._bound = []
+        if self.sink_name:
+            self.sink = tensors[self.sink_name].to(torch.float32).contiguous()
+            self._bound.append(self.sink)
         if self.qk_norm_eps is not None:
             self.q_norm_w = tensors[self.q_norm_name].to(torch.float32).contiguous()
-            self._bound = [self.q_norm_w]
+            self._bound.append(self.q_norm_w)
             if not self.shares_kv:
                 self.k_norm_w = tensors[self.k_norm_name].to(torch.float32).contiguous()
                 self._bound.append(self.k_norm_w)
@@ -93,14 +124,14 @@ class GQAttention(Mixer):
             # q only: head norm and rotation over the q heads, nothing written to the cache
             kernels.qk_prepare(proj, self.q_norm_w, None, self.position.rate_table(), batch.tok_pos, batch.tok_seq,
                                batch.seq_slot, batch.seq_end, None, 0, None, 0, QH, 0, HD, self.qk_norm_eps or 0.0,
-                               interleaved=interleaved)
+                               interleaved=interleaved, q_temp=self.q_temp)
             gate = proj[:, QS:] if self.output_gate else None
         else:
             # an append step keeps the cache as it is until its attention has run
             pool = None if batch.append else state.pool
             kernels.qk_prepare(proj, self.q_norm_w, self.k_norm_w, self.position.rate_table(), batch.tok_pos,
                                batch.tok_seq, batch.seq_slot, batch.seq_end, pool, state.pages, state.ptab,
-                               state.ring, QH, KVH, HD, self.qk_norm_eps or 0.0, interleaved=interleaved)
+                               state.ring, QH, KVH, HD, self.qk_norm_eps or 0.0, interleaved=interleaved, q_temp=self.q_temp)
             gate = proj[:, QS + 2 * KVS:] if self.output_gate else None
         q = proj[:, :QS]
         ctx = torch.empty((batch.T, QS), dtype=x.dtype, device=x.device)
@@ -121,12 +152,12 @@ class GQAttention(Mixer):
                 k, v = proj[:, QS:QS + KVS], proj[:, QS + KVS:QS + 2 * KVS]
                 batch.shared[("kv", state.unit)] = (k, v)
             if batch.append:
-                rt.attention_append(ctx, q, k, v, gate, batch, state, QH, KVH, HD, self.window, self.scale)
+                rt.attention_append(ctx, q, k, v, gate, batch, state, QH, KVH, HD, self.window, self.scale, sink=self.sink)
                 if not self.shares_kv:
                     kernels.kv_store(proj[:, QS:QS + 2 * KVS], batch.tok_pos, batch.tok_seq, batch.seq_slot,
                                      batch.seq_end, state.pool, state.pages, state.ptab, state.ring, KVH, HD)
             else:
-                rt.attention_prefill(ctx, q, k, v, gate, batch, QH, KVH, HD, self.window, self.scale)
+                rt.attention_prefill(ctx, q, k, v, gate, batch, QH, KVH, HD, self.window, self.scale, sink=self.sink)
         else:
             # launched for the longest sequence that this step's length class allows, so that a
             # recording of the step serves every step of the class
@@ -134,8 +165,8 @@ class GQAttention(Mixer):
             n_chunks = max(1, -(-entries // ATTN_DECODE_CHUNK))
             part_o, part_ml = rt.scratch_attn_decode(batch.B, QH, HD, n_chunks)
             kernels.attn_decode(ctx, q, gate, batch.seq_pos0, batch.seq_slot, state.pool, state.pages, state.ptab,
-                                state.ring, self.window, QH, KVH, HD, n_chunks, self.scale, part_o, part_ml)
-        return self.out.apply(rt, ctx, partial_ok=batch.partial_sums_ok)
+                                state.ring, self.window, QH, KVH, HD, n_chunks, self.scale, part_o, part_ml, sink=self.sink)
+        return self.out.apply(rt, ctx, out_dtype=self.out_dtype, partial_ok=batch.partial_sums_ok and self.out_dtype is None)
 
 
 register_part("mixer", "gqa_attention", GQAttention)

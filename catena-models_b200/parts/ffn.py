@@ -14,7 +14,11 @@ class SwiGLU(FeedForward):
     fused_decode_ok = True
     supports_append = True
 
-    def __init__(self, prefix, hidden, intermediate, names=None):
+    def __init__(self, prefix, hidden, intermediate, names=None, out_dtype=None):
+        """out_dtype "float32": the down projection's result stays in float (for a float residual stream)."""
+        import torch
+
+        self.out_dtype = {None: None, "float32": torch.float32}[out_dtype]
         names = names or {}
         n = lambda key, default: prefix + names.get(key, default)
         self.hidden, self.intermediate = hidden, intermediate
@@ -27,7 +31,7 @@ class SwiGLU(FeedForward):
 
     def forward(self, rt, batch, x):
         a = rt.gate_up_swiglu(x, self.gate_up.weight, self.intermediate)
-        return self.down.apply(rt, a, partial_ok=batch.partial_sums_ok)
+        return self.down.apply(rt, a, out_dtype=self.out_dtype, partial_ok=batch.partial_sums_ok and self.out_dtype is None)
 
 
 register_part("feed_forward", "swiglu", SwiGLU)

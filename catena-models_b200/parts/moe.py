@@ -1,0 +1,87 @@
+"""Routed feed-forward: `experts` small gated feed-forward layers of which every token uses `top`.
+
+Router logits z = W_r h and the scores (sigmoid of each logit, or a softmax over the experts) are float32;
+the `top` largest scores are chosen (the lower index among equals) and are the weights, as they are or
+divided by their sum (`renormalize`).  `weight_on` says where a weight goes: "input" runs the expert on
+weight * h and adds the outputs, "output" runs it on h and adds weight * output.  An expert is
+W_down (act(W_gate x) * (W_up x)), act = silu or tanh-gelu.
+
+Routing, the ordering of the (token, choice) pairs by expert and the experts' products all run on the
+device from what the router kernel leaves there, so the part launches the same kernels for every step of
+a shape and its steps can be recorded.  The result is one float32 row per pair; the block's residual sum
+adds a token's rows in the order of its choices.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..weights.loader import TensorSpec
+from .base import FeedForward, register_part
+
+
+class RoutedSwiGLU(FeedForward):
+    prompt_capturable = True
+    supports_append = True
+
+    def __init__(self, prefix, hidden, intermediate, experts, top, gate="sigmoid", renormalize=False,
+                 weight_on="input", activation="silu", expert_name="e{}."):
+        if gate not in ("sigmoid", "softmax") or weight_on not in ("input", "output") or activation not in ("silu", "gelu_tanh"):
+            raise ValueError("RoutedSwiGLU: gate sigmoid|softmax, weight_on input|output, activation silu|gelu_tanh")
+        if not 1 <= top <= experts:
+            raise ValueError(f"RoutedSwiGLU: {top} of {experts} experts")
+        self.prefix, self.hidden, self.intermediate = prefix, hidden, intermediate
+        self.experts, self.top = experts, top
+        self.softmax_gate, self.renormalize = gate == "softmax", bool(renormalize)
+        self.weight_on_input, self.gelu = weight_on == "input", activation == "gelu_tanh"
+        self.expert_name = expert_name
+
+    def _names(self, e):
+        q = self.prefix + self.expert_name.format(e)
+        return q + "gate", q + "up", q + "down"
+
+    def tensor_specs(self):
+        H, F = self.hidden, self.intermediate
+        specs = [TensorSpec(self.prefix + "router", (self.experts, H))]
+        for e in range(self.experts):
+            g, u, d = self._names(e)
+            specs += [TensorSpec(g, (F, H)), TensorSpec(u, (F, H)), TensorSpec(d, (H, F))]
+        return specs
+
+    def bind(self, tensors, rt):
+        names = [self._names(e) for e in range(self.experts)]
+        self.router = tensors[self.prefix + "router"].contiguous()
+        # [E, 2 F, H]: an expert's gate rows, then its up rows; [E, H, F]
+        self.w_up = torch.stack([torch.cat([tensors[g], tensors[u]], 0) for g, u, _ in names]).contiguous()
+        self.w_down = torch.stack([tensors[d] for _, _, d in names]).contiguous()
+        if self.router.dtype != self.w_up.dtype:
+            self.router = self.router.to(self.w_up.dtype)
+        self._bound = [self.router]
+
+    def weight_bytes(self):
+        # a step reads the router and, of the experts, what its tokens choose: at most every expert once
+        per_expert = (self.w_up[0].numel() + self.w_down[0].numel()) * self.w_up.element_size()
+        return self.router.numel() * self.router.element_size() + self.experts * per_expert
+
+    def forward(self, rt, batch, x):
+        T, top, E = x.shape[0], self.top, self.experts
+        P = T * top
+        dev = x.device
+        if x.dtype != self.w_up.dtype:
+            raise ValueError("RoutedSwiGLU: activations and expert matrices must share a dtype")
+        max_tiles = kernels.moe_max_tiles(P, E)
+        ids = torch.empty(P, dtype=torch.int32, device=dev)
+        wts = torch.empty(P, dtype=torch.float32, device=dev)
+        perm = torch.empty(P, dtype=torch.int32, device=dev)
+        work = torch.empty(2 * E + 1 + 3 * max_tiles, dtype=torch.int32, device=dev)
+        kernels.moe_route(ids, wts, perm, work, x, self.router, batch.tok_seq, top, self.softmax_gate, self.renormalize)
+        a = torch.empty((P, self.intermediate), dtype=x.dtype, device=dev)
+        kernels.moe_grouped(a, x, self.w_up, work, perm, wts, top, max_tiles, up=True,
+                            apply_weight=self.weight_on_input, gelu=self.gelu)
+        y = torch.empty((P, self.hidden), dtype=torch.float32, device=dev)
+        kernels.moe_grouped(y, a, self.w_down, work, perm, wts, top, max_tiles, up=False,
+                            apply_weight=not self.weight_on_input)
+        return kernels.Terms([(y, 1.0, top)])
+
+
+register_part("feed_forward", "routed_swiglu", RoutedSwiGLU)

@@ -19,8 +19,11 @@ class RMSNorm(Norm):
     supports_append = True
     fused_kind = "rms"          # what the fused residual kernel can absorb
 
-    def __init__(self, name, width, eps):
+    def __init__(self, name, width, eps, weight_offset=0.0):
+        """weight_offset: what is added to the stored weight (1 for a checkpoint that stores the distance
+        of the weight from one); the sum is formed once, in float, when the tensor is bound."""
         self.name, self.width, self.eps = name, width, float(eps)
+        self.weight_offset = float(weight_offset)
         self.weight = None
 
     def tensor_specs(self):
@@ -28,9 +31,16 @@ class RMSNorm(Norm):
 
     def bind(self, tensors, rt):
         self.weight = tensors[self.name].to(torch.float32).contiguous()
+        if self.weight_offset:
+            self.weight = self.weight + self.weight_offset
         self._bound = [self.weight]
 
     def apply(self, rt, x):
+        if x.dtype == torch.float32 and (rt.dtype != torch.float32 or self.width % 8):
+            # rows of a float residual stream: normed in float, written as activations
+            y = torch.empty(x.shape, dtype=rt.dtype, device=x.device)
+            kernels.norm_f32in(y, x, self.weight, self.eps)
+            return y
         y = torch.empty_like(x)
         kernels.rmsnorm(y, x, self.weight, self.eps)
         return y

@@ -1,0 +1,141 @@
+"""Mixers that keep a matrix per head as their state and carry it from token to token.
+
+`DecayMix` (time mixing in the manner of RWKV-6): every projection reads its own blend of the present
+and the previous token's input, x_s = h + (h_prev - h) * mu_s; receptance r, key k, value v (heads x dim)
+and an output gate silu(W_g x_g); a decay per token, head and key channel, w = exp(-exp(W_2 tanh(W_1 x_w)
++ w_0)); per head
+
+    o_t = (S_(t-1) + diag(u) k_t v_t^T)^T r_t        S_t = diag(w_t) S_(t-1) + k_t v_t^T
+
+with the bonus u for the present token only; each head's o is brought to unit root mean square, then
+times a channel weight and the gate, then the output projection.  State per sequence: the previous
+token's input and S, float32.
+
+`MatrixMemory` (the mLSTM cell of xLSTM): q = W_q h / sqrt(dim), k, v; per head a log input gate
+i = cap tanh((W_i h + b_i) / cap) and a log forget gate f = log sigmoid(cap tanh((W_f h + b_f) / cap)); with
+a running maximum m that starts at 0
+
+    m_t = max(f + m_(t-1), i)     S_t = e^(f + m_(t-1) - m_t) S_(t-1) + e^(i - m_t) k v^T     n_t likewise with k
+    o = S_t^T q / (max(|n_t . q|, e^(-m_t)) + 1e-6)
+
+then the same unit norm, channel weight, sigmoid(W_g h) gate and output projection.  State: S, n, m, float32.
+
+Decays, gates, exponentials, the state and every sum over it are float32 whatever the activation dtype;
+the projections run through the runtime's products.  Both mixers run every kind of step through one
+kernel that starts from the stored state (zeros for a new sequence), so a prompt in one step, in portions
+or token by token gives the same numbers.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..cache.spec import FixedStateSpec
+from ..weights.loader import TensorSpec
+from .base import Mixer, register_part
+from .linear import Linear
+
+SCAN_SHARED_BYTES = 200 * 1024      # what the scan kernel may hold in shared memory (csrc/recurrent.cu)
+
+
+def scan_fits(dim, value_dim):
+    """True if a head's state of dim x value_dim floats fits the scan kernel's shared memory."""
+    ks = max(1, min(dim, 256 // max(1, value_dim)))
+    return value_dim <= 1024 and (dim * value_dim + 4 * dim + ks * value_dim) * 4 <= SCAN_SHARED_BYTES
+
+
+class DecayMix(Mixer):
+    prompt_capturable = True
+    supports_append = True
+
+    def __init__(self, prefix, hidden, heads, dim, rank, eps, out_dtype=None):
+        self.hidden, self.heads, self.dim, self.rank, self.eps = hidden, heads, dim, rank, float(eps)
+        self.size = heads * dim
+        self.prefix = prefix
+        self.proj = {s: Linear(prefix + s, self.size, hidden) for s in "rkvg"}
+        self.out = Linear(prefix + "o", hidden, self.size)
+        self.out_dtype = {None: None, "float32": torch.float32}[out_dtype]
+
+    def children(self):
+        return [*self.proj.values(), self.out]
+
+    def tensor_specs(self):
+        p, H, C = self.prefix, self.hidden, self.size
+        return ([TensorSpec(f"{p}mu.{s}", (H,), "vector") for s in "rkvgw"]
+                + [TensorSpec(p + "w1", (self.rank, H)), TensorSpec(p + "w2", (C, self.rank)),
+                   TensorSpec(p + "w0", (C,), "vector"), TensorSpec(p + "u", (self.heads, self.dim), "vector"),
+                   TensorSpec(p + "norm", (C,), "vector")])
+
+    def bind(self, tensors, rt):
+        p = self.prefix
+        f32 = lambda name: tensors[p + name].to(torch.float32).contiguous()
+        self.mu = torch.stack([f32("mu." + s) for s in "rkvgw"]).contiguous()
+        self.w1, self.w2 = tensors[p + "w1"].contiguous(), tensors[p + "w2"].contiguous()
+        self.w0, self.u, self.norm_w = f32("w0"), f32("u"), f32("norm")
+        self._bound = [self.mu, self.w1, self.w2, self.w0, self.u, self.norm_w]
+
+    def state_spec(self):
+        # the previous token's input, then S of every head
+        return FixedStateSpec((self.hidden + self.heads * self.dim * self.dim,), "float32")
+
+    def forward(self, rt, batch, x, state):
+        T, C = batch.T, self.size
+        mixes = torch.empty((5, T, self.hidden), dtype=x.dtype, device=x.device)
+        kernels.shift_mix(mixes, x, self.mu, state.tensor, batch.tok_seq, batch.tok_pos, batch.seq_pos0, batch.seq_slot)
+        r, k, v, g = (self.proj[s].apply(rt, mixes[i]) for i, s in enumerate("rkvg"))
+        decay = torch.empty((T, C), dtype=torch.float32, device=x.device)
+        kernels.lowrank_decay(decay, mixes[4], self.w1, self.w2, self.w0)
+        o = torch.empty((T, C), dtype=x.dtype, device=x.device)
+        kernels.matrix_scan("decay", o, r, k, v, g, decay, self.u, self.norm_w, state.tensor, self.hidden,
+                            batch.seq_start, batch.seq_slot, batch.B, self.heads, self.dim, self.dim, 1.0, self.eps,
+                            shift_src=x)
+        return self.out.apply(rt, o, out_dtype=self.out_dtype)
+
+
+class MatrixMemory(Mixer):
+    prompt_capturable = True
+    supports_append = True
+
+    def __init__(self, prefix, hidden, heads, dim, value_dim, gate_cap, eps, out_dtype=None):
+        self.hidden, self.heads, self.dim, self.value_dim = hidden, heads, dim, value_dim
+        self.gate_cap, self.eps, self.prefix = float(gate_cap), float(eps), prefix
+        self.k_size, self.v_size = heads * dim, heads * value_dim
+        # q | k | v | g in one product: they all read the same rows
+        self.qkvg = Linear([prefix + "q", prefix + "k", prefix + "v", prefix + "g"],
+                           [self.k_size, self.k_size, self.v_size, self.v_size], hidden)
+        self.gates = Linear([prefix + "i", prefix + "f"], [heads, heads], hidden)
+        self.out = Linear(prefix + "o", hidden, self.v_size)
+        self.out_dtype = {None: None, "float32": torch.float32}[out_dtype]
+
+    def children(self):
+        return [self.qkvg, self.gates, self.out]
+
+    def tensor_specs(self):
+        p = self.prefix
+        return [TensorSpec(p + "i.b", (self.heads,), "vector"), TensorSpec(p + "f.b", (self.heads,), "vector"),
+                TensorSpec(p + "norm", (self.v_size,), "vector")]
+
+    def bind(self, tensors, rt):
+        p = self.prefix
+        self.gate_bias = torch.cat([tensors[p + "i.b"], tensors[p + "f.b"]]).to(torch.float32).contiguous()
+        self.norm_w = tensors[p + "norm"].to(torch.float32).contiguous()
+        self._bound = [self.gate_bias, self.norm_w]
+
+    def state_spec(self):
+        # per head: S (dim x value_dim), n (dim), m
+        return FixedStateSpec((self.heads * (self.dim * self.value_dim + self.dim + 1),), "float32")
+
+    def forward(self, rt, batch, x, state):
+        T, KS, VS = batch.T, self.k_size, self.v_size
+        proj = self.qkvg.apply(rt, x)
+        gates = torch.empty((T, 2 * self.heads), dtype=torch.float32, device=x.device)
+        kernels.capped_gates(gates, x, self.gates.weight, self.gate_bias, self.gate_cap)
+        o = torch.empty((T, VS), dtype=x.dtype, device=x.device)
+        kernels.matrix_scan("memory", o, proj[:, :KS], proj[:, KS:2 * KS], proj[:, 2 * KS:2 * KS + VS],
+                            proj[:, 2 * KS + VS:], gates, None, self.norm_w, state.tensor, 0, batch.seq_start,
+                            batch.seq_slot, batch.B, self.heads, self.dim, self.value_dim, self.dim ** -0.5, self.eps)
+        return self.out.apply(rt, o, out_dtype=self.out_dtype)
+
+
+register_part("mixer", "decay_mix", DecayMix)
+register_part("mixer", "matrix_memory", MatrixMemory)

@@ -84,6 +84,20 @@ def open_folder(folder):
     return files, table
 
 
+def tensor_shapes(folder):
+    """{name: shape} of everything the folder's file(s) hold: for a configuration that leaves a size to the
+    tensors (`with_tensor_shapes`)."""
+    try:
+        files, table = open_folder(folder)
+    except SafetensorsError as exc:
+        raise WeightError(folder, other=[str(exc)]) from exc
+    try:
+        return {name: tuple(f.info(name)[1]) for name, f in table.items()}
+    finally:
+        for f in files.values():
+            f.close()
+
+
 def _target_dtype(stored, role, widen):
     """The dtype a tensor is kept in, or None when the stored dtype cannot be used."""
     if role == "table":
