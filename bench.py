@@ -512,6 +512,142 @@ def kernel_table(model, cfg, pk, batch, context, prompt_lengths, graph_ms):
                   f"{gbs:.0f} | {gbs / pk['hbm_gbs']:.2f} | {tf:.1f} | {tf / pk['bf16_tflops']:.3f} |")
 
 
+# ---------------------------------------------------------------------- another design beside LFM3
+# Sizes that resemble a real model's layers, for `--compare narasun`: the Narasun decoder (an attention with a
+# sink beside a decay mix, matrix memories, dense and routed feed-forwards; two of its layers looped twice) and
+# an LFM3 decoder of the same width, layer count, attention heads and dense feed-forward width.
+COMPARE_SIZES = {
+    "1024": dict(width=1024, heads=16, kv_heads=4, head=64, mix_heads=16, mix_dim=64, rank=64, mem_heads=8, mem_dim=64,
+                 mem_vdim=128, ff=4096, expert_ff=1024, experts=8, top=2),
+    "2048": dict(width=2048, heads=32, kv_heads=8, head=64, mix_heads=32, mix_dim=64, rank=64, mem_heads=16, mem_dim=64,
+                 mem_vdim=128, ff=8192, expert_ff=2048, experts=8, top=2),
+}
+
+
+def narasun_config(size, vocab=VOCAB):
+    z = COMPARE_SIZES[size]
+    par = lambda mlp: dict(type="parallel", mlp=mlp, mixer=dict(
+        left=dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["head"], vdim=z["head"], scale=z["head"] ** -0.5,
+                  q_temp=dict(coef=0.5, every=256)),
+        right=dict(heads=z["mix_heads"], dim=z["mix_dim"], rank=z["rank"]), left_scale=0.8, right_scale=0.9))
+    mem = lambda mlp, kind="mlstm": dict(type=kind, mlp=mlp, mixer=dict(heads=z["mem_heads"], dim=z["mem_dim"],
+                                                                         vdim=z["mem_vdim"], gate_cap=15.0))
+    dense = dict(kind="dense", ff=z["ff"])
+    moe = dict(kind="moe", expert=dict(ff=z["expert_ff"]), router=dict(experts=z["experts"], top=z["top"]))
+    # six layers, the middle two run twice: eight layer runs (four of each mixer, four of each feed-forward)
+    layers = [par(dense), mem(moe), par(moe), mem(dense, "mlstm_2"), par(dense), mem(moe)]
+    return dict(architecture="Narasun", vocab=vocab, width=z["width"], norm=dict(eps=1e-6), layers=layers,
+                loop=dict(start=2, stop=4, times=2))
+
+
+def lfm3_like_config(size, vocab=VOCAB):
+    z = COMPARE_SIZES[size]
+    return dict(architecture="lfm3", vocab_size=vocab, hidden_size=z["width"], intermediate_size=z["ff"], num_hidden_layers=8,
+                layer_types=["conv", "full_attention"] * 4, num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"],
+                head_dim=z["head"], conv_L_cache=3, sliding_window=4096, rope_theta=1000000.0, norm_eps=1e-5,
+                tie_word_embeddings=False, max_position_embeddings=8192)
+
+
+def _timed_steps(torch, model, prompt_len, batch, steps, vocab):
+    """(prompt step ms, decode step ms) of a model: one prompt of `prompt_len` tokens alone (median of three runs
+    after one untimed), then `batch` sequences at that context decoding `steps` steps after eight untimed."""
+    eng = model.engine
+    toks, state = synthetic_tokens(prompt_len, vocab)
+    times = []
+    for i in range(4):
+        (slot,) = eng.admit(1)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        eng.step([slot], [toks])
+        b.record()
+        torch.cuda.synchronize()
+        eng.release([slot])
+        if i:
+            times.append(a.elapsed_time(b))
+    prompts = []
+    for _ in range(batch):
+        p, state = synthetic_tokens(prompt_len, vocab, state)
+        prompts.append(p)
+    run = decode_run(model, prompts, steps, 8, vocab, state)
+    return statistics.median(times), run["ms_per_step"], run["launches"] / steps
+
+
+def _print_kernel_rows(title, rows, step_us, pk):
+    total = sum(r["us"] for r in rows)
+    print(f"\n### {title}\n")
+    print(f"the step takes {step_us:.0f} us on the stream; the kernels' own times add up to {total:.0f} us.  Peaks "
+          f"({pk['source']}): {pk['hbm_gbs']:.0f} GB/s, {pk['bf16_tflops']:.0f} TFLOP/s.\n")
+    print("| kernel | operands | calls | us | share | GB/s | of peak | TFLOP/s | of peak |")
+    print("|---|---|---|---|---|---|---|---|---|")
+    for r in sorted(rows, key=lambda r: -r["us"]):
+        sec = r["us"] * 1e-6
+        gbs = r["bytes"] / sec / 1e9 if r["bytes"] else 0.0
+        tf = r["flops"] / sec / 1e12 if r["flops"] else 0.0
+        print(f"| {r['name']} | {r['shape']} | {r['calls']} | {r['us']:.1f} | {r['us'] / total:.3f} | "
+              f"{gbs:.0f} | {gbs / pk['hbm_gbs']:.2f} | {tf:.1f} | {tf / pk['bf16_tflops']:.3f} |")
+
+
+def _kernel_rows(torch, model, prompt_len, batch, vocab):
+    """Kernel by kernel (an event pair around every launch): one prompt step and one decode step of a fresh engine."""
+    from catena_models_b200 import kernels
+    from catena_models_b200.engine.engine import Engine
+
+    eng = Engine(model.decoder, batch * (prompt_len + 64), batch, use_graphs=False)
+    toks, state = synthetic_tokens(prompt_len, vocab)
+    out = {}
+    for rep in range(2):
+        slots = eng.admit(batch)
+        for s in slots[1:]:
+            eng.step([s], [toks], [[]])
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with kernels.Timeline() as tl:
+            a.record()
+            eng.step(slots[:1], [toks])
+            b.record()
+        out["prompt"] = (tl.rows(), a.elapsed_time(b) * 1e3)
+        with kernels.Timeline() as tl:
+            a.record()
+            eng.step(slots, [[1]] * batch)
+            b.record()
+        out["decode"] = (tl.rows(), a.elapsed_time(b) * 1e3)
+        eng.release(slots)
+    eng.check_errors()
+    return out
+
+
+def compare_designs(sizes, prompt_len, batch, steps, pk, tables):
+    """Prefill and decode throughput of the Narasun decoder beside an LFM3 decoder of equal size, random weights."""
+    import torch
+
+    from catena_models_b200.api import Model
+
+    vocab = 32768
+    print(f"prompt step: one prompt of {prompt_len} tokens; decode: {batch} sequences at {prompt_len} tokens, {steps} timed "
+          f"steps (recorded graphs, on-device argmax); bfloat16, random weights, one B200.\n")
+    print("| width | model | parameters | weights read per decode step | prompt step ms | prompt tok/s | decode step ms | decode tok/s | "
+          "of copy bandwidth | kernels per decode step |")
+    print("|---|---|---|---|---|---|---|---|---|---|")
+    for size in sizes:
+        for name, cfg in (("Narasun", narasun_config(size, vocab)), ("LFM3", lfm3_like_config(size, vocab))):
+            model = Model.random(cfg, seed=0, std=0.02, dtype="bfloat16", max_tokens=batch * (prompt_len + 256) + 4096,
+                                 max_seqs=batch + 1)
+            p_ms, d_ms, launches = _timed_steps(torch, model, prompt_len, batch, steps, vocab)
+            wb = model.decoder.weight_bytes_per_step()
+            print(f"| {size} | {name} | {model.parameter_count() / 1e6:.0f} M | {wb / 1e6:.0f} MB | {p_ms:.2f} | "
+                  f"{prompt_len / p_ms * 1e3:,.0f} | {d_ms:.3f} | {batch / d_ms * 1e3:,.0f} | "
+                  f"{wb / (d_ms * 1e-3) / 1e9 / pk['hbm_gbs']:.2f} | {launches:.0f} |", flush=True)
+            if tables:
+                rows = _kernel_rows(torch, model, prompt_len, batch, vocab)
+                for key, title in (("prompt", f"{name} {size}: prompt step, {prompt_len} tokens"),
+                                   ("decode", f"{name} {size}: decode step, {batch} sequences at {prompt_len}")):
+                    _print_kernel_rows(title, rows[key][0], rows[key][1], pk)
+                print()
+            del model
+            torch.cuda.empty_cache()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -533,6 +669,11 @@ def main():
                     help="time one decode step and one prompt step kernel by kernel and print the table")
     ap.add_argument("--attention-table", action="store_true",
                     help="time the prompt-attention kernels alone at 2,048, 4,096 and 16,384 tokens and print the table")
+    ap.add_argument("--compare", default=None, choices=["narasun"],
+                    help="instead of the JSON line: prompt and decode throughput of that design beside an LFM3 decoder of "
+                         "equal size (random weights), as a table")
+    ap.add_argument("--compare-sizes", default="1024,2048", help="widths of `--compare`")
+    ap.add_argument("--compare-kernels", action="store_true", help="with `--compare`: also each model's kernel tables")
     ap.add_argument("--print-config", action="store_true",
                     help="print the configuration's config.json (for `python -m catena_models_b200 --random FILE`) and exit")
     args = ap.parse_args()
@@ -544,6 +685,10 @@ def main():
         print(json.dumps({"impl": "reference", "unavailable":
                           "catena-models is a Rust crate whose kernel compiler is a network git dependency; "
                           "no Rust toolchain, no network and no GGUF checkpoint here, and pip finds no Python project in it"}))
+        return 0
+    if args.compare and args.gpus == 1:
+        compare_designs(args.compare_sizes.split(","), args.prompt_len or 2048, args.batch or 8, min(args.steps, 64), peaks(),
+                        args.compare_kernels)
         return 0
     if args.gpus != 1:
         print(json.dumps({"error": "this engine runs on one GPU; --gpus %d is not supported" % args.gpus,

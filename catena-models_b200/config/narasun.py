@@ -206,11 +206,11 @@ class NarasunConfig:
                 if -(-max(a.dim, a.vdim) // 16) * 16 > limits.MAX_HEAD_DIM:
                     problems.append(f"layers[{i}]: attention heads of {max(a.dim, a.vdim)}: the kernels take up to {limits.MAX_HEAD_DIM}")
                 if not scan_fits(d.dim, d.dim):
-                    problems.append(f"layers[{i}]: a decay-mix state of {d.dim} x {d.dim} does not fit the scan kernel")
+                    problems.append(f"layers[{i}]: decay-mix heads of {d.dim} channels: the scan kernel takes up to 1024")
             else:
                 m = layer.mixer
                 if not scan_fits(m.dim, m.vdim):
-                    problems.append(f"layers[{i}]: a matrix memory of {m.dim} x {m.vdim} does not fit the scan kernel")
+                    problems.append(f"layers[{i}]: matrix-memory heads of {m.dim} key channels: the scan kernel takes up to 1024")
             if layer.mlp is not None and layer.mlp.kind == "moe" and layer.mlp.top > layer.mlp.experts:
                 problems.append(f"layers[{i}]: top {layer.mlp.top} of {layer.mlp.experts} experts")
         if self.loop is not None and not 0 <= self.loop.start < self.loop.stop <= len(self.layers):

@@ -5,12 +5,12 @@
 //   matrix memory  m' = max(f + m, i) ;  S <- e^(f + m - m') S + e^(i - m') k v^T ;  n likewise with k alone ;
 //                  o = S^T q / (max(|n . q|, e^(-m')) + 1e-6)         (log-domain gates i, f with a running maximum m)
 //
-// followed, in the same kernel, by the unit norm of each head's output, the channel weights and the output
-// gate.  State, gates, decays and all sums are float whatever the activation type.  The state lives in
-// per-slot rows of a float array; a step starts from what is stored there (zeros for a new sequence) and
-// leaves its last state, so whole prompts, portions of prompts and single tokens run the same code and
-// give the same numbers.  One block owns one head of one sequence and walks the sequence's rows of the
-// step in order; rows that belong to no sequence (padding) are never touched.
+// followed by the unit norm of each head's output, the channel weights and the output gate.  State, gates,
+// decays and all sums are float whatever the activation type.  The state lives in per-slot rows of a float
+// array; a step starts from what is stored there (zeros for a new sequence) and leaves its last state, so
+// whole prompts, portions of prompts and single tokens run the same code and give the same numbers.  A block
+// owns some columns of one head's state for one sequence and walks the sequence's rows of the step in order;
+// rows that belong to no sequence (padding) are never touched.
 //
 // Beside it: the token shift (each projection reads its own blend of the present and the previous
 // token's input), the low-rank decay network, and the capped gate pre-activations.
@@ -69,6 +69,22 @@ __device__ __forceinline__ void warp_row_dots(const T* __restrict__ wrow, const 
     const int lane = threadIdx.x & 31;
 #pragma unroll
     for (int r = 0; r < RP_ROWS; ++r) acc[r] = 0.f;
+    if (W % 8 == 0 && ldx % 8 == 0) {                  // 16-byte accesses: eight columns a lane and round
+        for (int c = lane * 8; c < W; c += 256) {
+            float wv[8], xv[8];
+            load8f<T>(wrow + c, wv);
+#pragma unroll
+            for (int r = 0; r < RP_ROWS; ++r)
+                if (r < n_rows) {
+                    load8f<T>(x + r * ldx + c, xv);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[r] = fmaf(wv[i], xv[i], acc[r]);
+                }
+        }
+#pragma unroll
+        for (int r = 0; r < RP_ROWS; ++r) acc[r] = warp_sum(acc[r]);
+        return;
+    }
     for (int c = lane; c < W; c += 32) {
         const float wv = to_f32(wrow[c]);
 #pragma unroll
@@ -80,7 +96,8 @@ __device__ __forceinline__ void warp_row_dots(const T* __restrict__ wrow, const 
 }
 
 // Decay of the decay mix: w = exp(-exp(W2 tanh(W1 x) + w0)), per token and channel, in float.
-// x [rows][W], W1 [R][W], W2 [C][R], w0 [C]; out [rows][C] float.
+// x [rows][W], W1 [R][W], W2 stored transposed [R][C] (neighbouring threads read neighbouring channels), w0 [C];
+// out [rows][C] float.
 template <typename T>
 __global__ void __launch_bounds__(RP_THREADS)
 lowrank_decay_kernel(float* __restrict__ out, const T* __restrict__ x, const T* __restrict__ w1,
@@ -101,8 +118,7 @@ lowrank_decay_kernel(float* __restrict__ out, const T* __restrict__ x, const T* 
     for (int e = threadIdx.x; e < n_rows * C; e += RP_THREADS) {
         const int i = e / C, c = e - i * C;
         float z = 0.f;
-        const T* wr = w2 + (long long)c * R;
-        for (int r = 0; r < R; ++r) z = fmaf(to_f32(wr[r]), th[i * R + r], z);
+        for (int r = 0; r < R; ++r) z = fmaf(to_f32(w2[(long long)r * C + c]), th[i * R + r], z);
         out[(row0 + i) * C + c] = expf(-expf(z + w0[c]));
     }
 }
@@ -180,140 +196,291 @@ struct ScanArgs {
     const int *seq_start, *seq_slot;
     int H, D, DV, KS;
     float q_scale, eps;
+    float* raw;                       // [rows][H * DV] float: the heads' outputs before norm and gate
+    long long rows;
 };
 
-// MODE 0: decay mix.  MODE 1: matrix memory.  Thread (j, ks) owns column j of S for the key channels
-// ks, ks + KS, ...; the KS partial outputs of a column are added in index order.
-template <typename T, int MODE>
-__global__ void matrix_scan_kernel(const ScanArgs a) {
-    extern __shared__ float sm[];
-    __shared__ float scratch[32];
+#define SCAN_THREADS 128
+#define SCAN_MAX_ROWS 32          // rows of the step that a block stages at a time
+
+template <int N>
+__device__ __forceinline__ void load_run(const float* p, float* out) {
+    if constexpr (N % 4 == 0) {
+#pragma unroll
+        for (int x = 0; x < N; x += 4) {
+            const float4 t = *reinterpret_cast<const float4*>(p + x);
+            out[x] = t.x; out[x + 1] = t.y; out[x + 2] = t.z; out[x + 3] = t.w;
+        }
+    } else {
+#pragma unroll
+        for (int x = 0; x < N; x += 2) {
+            const float2 t = *reinterpret_cast<const float2*>(p + x);
+            out[x] = t.x; out[x + 1] = t.y;
+        }
+    }
+}
+
+// MODE 0: decay mix.  MODE 1: matrix memory.  A block owns some columns of one head's S for one sequence and
+// walks the sequence's rows of the step in order.  Thread (column c, part ks) keeps S[i][c] for the RPT key
+// channels i = ks * RPT ... in registers.  For the matrix memory the block's last column is the normaliser n: it
+// is the column of S whose value channel is constantly one (n <- a n + b k, and its output is n . q), so it needs
+// no code of its own; every block keeps a copy, and all copies see the same operations.
+// The block stages the operands of up to SCAN_MAX_ROWS rows in shared memory at a time (as floats: q times its
+// scale, k, the decay, its columns of v), so the latency of global memory is paid once per group of rows.  For the
+// matrix memory the first warp then walks the gates of the group (the running maximum is a chain; the
+// exponentials of all rows are formed side by side).  The walk of the state over the group needs no barrier, no
+// exchange and no exponential: a thread leaves its part of every row's output in shared memory, and once the
+// group is through, the parts of a column are added in index order and divided by the normaliser.  Columns do
+// not depend on each other, so the split over blocks changes no number, and an element of S sees the same
+// operations in the same order whatever the number of parts.  Outputs go to `raw` in float; the unit norm over a
+// head's columns, the channel weights and the gate follow in head_norm_gate_kernel.
+template <typename T, int MODE, int RPT>
+__global__ void __launch_bounds__(SCAN_THREADS)
+matrix_scan_kernel(const ScanArgs a, int TB) {
+    extern __shared__ __align__(16) float sm[];
     pdl_trigger();
     pdl_wait();
-    const int hd = blockIdx.x, b = blockIdx.y;
+    const int hd = blockIdx.x, cb = blockIdx.y, b = blockIdx.z;
     const int s0 = a.seq_start[b], s1 = a.seq_start[b + 1];
     if (s1 <= s0) return;
     const int D = a.D, DV = a.DV, KS = a.KS, H = a.H;
-    float* S = sm;                       // [D][DV]
-    float* qv = S + D * DV;              // [D] query / receptance
-    float* kv = qv + D;                  // [D] key
-    float* wv = kv + D;                  // [D] decay (MODE 0) / normaliser n (MODE 1)
-    float* uv = wv + D;                  // [D] bonus (MODE 0)
-    float* part = uv + D;                // [KS][DV]
-    const int tid = threadIdx.x, nt = blockDim.x;
-    const int j = tid % DV, ks = tid / DV;
-    const bool active = ks < KS;
+    const int Dp = KS * RPT;                          // a staged row's pitch: the parts' runs of channels, D <= Dp
+    const int cols = SCAN_THREADS / KS;               // columns of the block, the normaliser's among them
+    const int real = MODE == 1 ? cols - 1 : cols;     // columns of S proper
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int ks = threadIdx.x % KS, c = threadIdx.x / KS, j = cb * real + c;
+    const bool is_n = MODE == 1 && c == real;
+    const bool active = is_n || j < DV;
+    const int i0 = ks * RPT;
+    float* sq = sm;                                   // [TB][Dp]
+    float* sk = sq + (size_t)TB * Dp;                 // [TB][Dp]
+    float* sw = sk + (size_t)TB * Dp;                 // [TB][Dp]  (MODE 0)
+    float* sv = sw + (MODE == 0 ? (size_t)TB * Dp : 0);   // [TB][cols]
+    float* sg = sv + (size_t)TB * cols;               // [TB][4]: MODE 1: a = e^(f + m - m'), b = e^(i - m'), e^(-m')
+    float* part = sg + (size_t)TB * 4;                // [TB][KS][cols] partial outputs
     const long long per_head = (long long)D * DV + (MODE == 1 ? D + 1 : 0);
     float* st = a.state + (long long)a.seq_slot[b] * a.state_stride + a.state_offset + hd * per_head;
-    for (int e = tid; e < D * DV; e += nt) S[e] = st[e];
-    float m = 0.f;
-    if (MODE == 1) {
-        for (int e = tid; e < D; e += nt) wv[e] = st[D * DV + e];
-        m = st[D * DV + D];
-    } else {
-        for (int e = tid; e < D; e += nt) uv[e] = a.bonus[hd * D + e];
+    float S[RPT], U[RPT];
+#pragma unroll
+    for (int it = 0; it < RPT; ++it) {
+        const int i = i0 + it;
+        S[it] = (active && i < D) ? (is_n ? st[(long long)D * DV + i] : st[(long long)i * DV + j]) : 0.f;
+        U[it] = (MODE == 0 && i < D) ? a.bonus[hd * D + i] : 0.f;
     }
+    float m = MODE == 1 ? st[(long long)D * DV + D] : 0.f;      // the first warp carries it
     const T* Q = (const T*)a.q + (long long)hd * D;
     const T* K = (const T*)a.k + (long long)hd * D;
-    const T* V = (const T*)a.v + (long long)hd * DV;
-    const T* G = (const T*)a.g + (long long)hd * DV;
-    T* O = (T*)a.out + (long long)hd * DV;
-    const float nw = active && ks == 0 ? a.norm_w[hd * DV + j] : 0.f;
-    for (long long t = s0; t < s1; ++t) {
-        __syncthreads();                 // the vectors of the row before are no longer read; S and n are loaded
-        for (int e = tid; e < D; e += nt) {
-            qv[e] = to_f32(Q[t * a.ldq + e]) * a.q_scale;
-            kv[e] = to_f32(K[t * a.ldk + e]);
-            if (MODE == 0) wv[e] = a.decay[t * ((long long)H * D) + hd * D + e];
-        }
-        const float vj = active ? to_f32(V[t * a.ldv + j]) : 0.f;
-        float af = 1.f, bi = 1.f;
-        if (MODE == 1) {
-            const float ig = a.decay[t * 2 * H + hd], fg = a.decay[t * 2 * H + H + hd];
-            const float m_new = fmaxf(fg + m, ig);
-            af = expf(fg + m - m_new);
-            bi = expf(ig - m_new);
-            m = m_new;
-        }
-        __syncthreads();
-        float acc = 0.f;
-        if (active) {
-            for (int i = ks; i < D; i += KS) {
-                const float s = S[i * DV + j], x = kv[i] * vj;
-                if (MODE == 0) {
-                    acc = fmaf(fmaf(uv[i], x, s), qv[i], acc);
-                    S[i * DV + j] = fmaf(wv[i], s, x);
-                } else {
-                    const float s2 = fmaf(af, s, bi * x);
-                    S[i * DV + j] = s2;
-                    acc = fmaf(s2, qv[i], acc);
+    const T* V = (const T*)a.v + (long long)hd * DV + (long long)cb * real;
+    const float* Wd = a.decay + (MODE == 0 ? (long long)hd * D : 0);
+    const long long ldw = MODE == 0 ? (long long)H * D : 2LL * H;
+    float* R = a.raw + (long long)hd * DV + (long long)cb * real;
+    const long long ldr = (long long)H * DV;
+    const int n_cols = max(0, min(real, DV - cb * real));
+    // 16-byte accesses to q, k and the decay: heads of a multiple of 8 channels in rows and buffers aligned to match
+    const bool vec8 = D % 8 == 0 && a.ldq % 8 == 0 && a.ldk % 8 == 0 && (ldw % 8 == 0 || MODE == 1) &&
+                      (((uintptr_t)a.q | (uintptr_t)a.k) & 15) == 0 && (MODE == 1 || ((uintptr_t)a.decay & 31) == 0);
+    // channels past D of a staged row are read by the last part's vector accesses: they hold zeros
+    for (int e = threadIdx.x; e < TB * (Dp - D); e += SCAN_THREADS) {
+        const int tt = e / (Dp - D), i = D + e - tt * (Dp - D);
+        sq[(size_t)tt * Dp + i] = 0.f;
+        sk[(size_t)tt * Dp + i] = 0.f;
+        if (MODE == 0) sw[(size_t)tt * Dp + i] = 0.f;
+    }
+    for (long long t0 = s0; t0 < s1; t0 += TB) {
+        const int nt = (int)min((long long)TB, s1 - t0);
+        __syncthreads();                 // the group before is no longer read
+        if (vec8) {
+            // eight channels per access, four accesses of each operand in flight before the first is stored
+            const int D8 = D >> 3, n8 = nt * D8;
+            for (int e0 = threadIdx.x; e0 < n8; e0 += 4 * SCAN_THREADS) {
+                float fq[4][8], fk[4][8], fw[4][8];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int e = e0 + u * SCAN_THREADS;
+                    if (e < n8) {
+                        const int tt = e / D8, i = (e - tt * D8) * 8;
+                        load8f<T>(Q + (t0 + tt) * a.ldq + i, fq[u]);
+                        load8f<T>(K + (t0 + tt) * a.ldk + i, fk[u]);
+                        if (MODE == 0) load8f<float>(Wd + (t0 + tt) * ldw + i, fw[u]);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int e = e0 + u * SCAN_THREADS;
+                    if (e < n8) {
+                        const int tt = e / D8, i = (e - tt * D8) * 8;
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) fq[u][x] *= a.q_scale;
+                        store8f<float>(sq + (size_t)tt * Dp + i, fq[u]);
+                        store8f<float>(sk + (size_t)tt * Dp + i, fk[u]);
+                        if (MODE == 0) store8f<float>(sw + (size_t)tt * Dp + i, fw[u]);
+                    }
                 }
             }
-            part[ks * DV + j] = acc;
-        }
-        float den = 1.f;
-        if (MODE == 1) {
-            // n <- a n + b k, then n . q over the block in a fixed order
-            float dot = 0.f;
-            for (int e = tid; e < D; e += nt) {
-                const float n2 = fmaf(af, wv[e], bi * kv[e]);
-                wv[e] = n2;
-                dot = fmaf(n2, qv[e], dot);
-            }
-            dot = block_sum(dot, scratch);
-            den = fmaxf(fabsf(dot), expf(-m)) + 1e-6f;
         } else {
-            __syncthreads();
+            for (int e = threadIdx.x; e < nt * D; e += SCAN_THREADS) {
+                const int tt = e / D, i = e - tt * D;
+                sq[(size_t)tt * Dp + i] = to_f32(Q[(t0 + tt) * a.ldq + i]) * a.q_scale;
+                sk[(size_t)tt * Dp + i] = to_f32(K[(t0 + tt) * a.ldk + i]);
+                if (MODE == 0) sw[(size_t)tt * Dp + i] = Wd[(t0 + tt) * ldw + i];
+            }
         }
-        float o = 0.f;
-        if (active && ks == 0) {
-            for (int x = 0; x < KS; ++x) o += part[x * DV + j];
-            o /= den;
+        for (int e = threadIdx.x; e < nt * cols; e += SCAN_THREADS) {
+            const int tt = e / cols, cc = e - tt * cols;
+            sv[e] = (MODE == 1 && cc == real) ? 1.f : (cc < n_cols ? to_f32(V[(t0 + tt) * a.ldv + cc]) : 0.f);
         }
-        const float ss = block_sum(o * o, scratch);
-        if (active && ks == 0) {
-            const float inv = 1.f / sqrtf(ss / (float)DV + a.eps);
-            const float gz = to_f32(G[t * a.ldg + j]);
-            const float act = MODE == 0 ? gz * sigmoid_f32(gz) : sigmoid_f32(gz);
-            O[t * a.ldo + j] = from_f32<T>(((o * inv) * nw) * act);
+        if (MODE == 1 && warp == 0) {
+            // the gates of the group: lane tt fetches row tt's pair; the running maximum is a chain over the rows, which
+            // every lane walks (keeping its own row's values); the exponentials of all rows are then formed side by side
+            const float g_i = lane < nt ? Wd[(t0 + lane) * ldw + hd] : 0.f;
+            const float g_f = lane < nt ? Wd[(t0 + lane) * ldw + H + hd] : 0.f;
+            float mm = m, my_a = 0.f, my_b = 0.f, my_m = 0.f;
+            for (int tt = 0; tt < nt; ++tt) {
+                const float ig = __shfl_sync(0xffffffffu, g_i, tt), fg = __shfl_sync(0xffffffffu, g_f, tt);
+                const float m_new = fmaxf(fg + mm, ig);
+                if (tt == lane) {
+                    my_a = fg + mm - m_new;
+                    my_b = ig - m_new;
+                    my_m = -m_new;
+                }
+                mm = m_new;
+            }
+            if (lane < nt) {
+                sg[4 * lane] = expf(my_a);
+                sg[4 * lane + 1] = expf(my_b);
+                sg[4 * lane + 2] = expf(my_m);
+            }
+            m = mm;
+        }
+        __syncthreads();
+        // the state's walk over the group: no barrier, no exchange; a thread leaves its part of every row's output
+#pragma unroll 2
+        for (int tt = 0; tt < nt; ++tt) {
+            float q[RPT], k[RPT], w[RPT];
+            load_run<RPT>(sq + (size_t)tt * Dp + i0, q);
+            load_run<RPT>(sk + (size_t)tt * Dp + i0, k);
+            if (MODE == 0) load_run<RPT>(sw + (size_t)tt * Dp + i0, w);
+            const float vj = sv[tt * cols + c];
+            const float af = MODE == 1 ? sg[4 * tt] : 1.f, bv = MODE == 1 ? sg[4 * tt + 1] * vj : vj;
+            float acc = 0.f;
+#pragma unroll
+            for (int it = 0; it < RPT; ++it) {
+                const float x = k[it] * bv;
+                if (MODE == 0) {
+                    acc = fmaf(fmaf(U[it], x, S[it]), q[it], acc);
+                    S[it] = fmaf(w[it], S[it], x);
+                } else {
+                    S[it] = fmaf(af, S[it], x);
+                    acc = fmaf(S[it], q[it], acc);
+                }
+            }
+            part[((size_t)tt * KS + ks) * cols + c] = acc;
+        }
+        __syncthreads();
+        // a column's parts are added in index order; the matrix memory divides by its normaliser
+        for (int e = threadIdx.x; e < nt * real; e += SCAN_THREADS) {
+            const int tt = e / real, cc = e - tt * real;
+            if (cc >= n_cols) continue;
+            float o = 0.f;
+            for (int x = 0; x < KS; ++x) o += part[((size_t)tt * KS + x) * cols + cc];
+            if (MODE == 1) {
+                float dot = 0.f;
+                for (int x = 0; x < KS; ++x) dot += part[((size_t)tt * KS + x) * cols + real];
+                o /= fmaxf(fabsf(dot), sg[4 * tt + 2]) + 1e-6f;
+            }
+            R[(t0 + tt) * ldr + cc] = o;
         }
     }
-    __syncthreads();
-    for (int e = tid; e < D * DV; e += nt) st[e] = S[e];
+#pragma unroll
+    for (int it = 0; it < RPT; ++it) {
+        const int i = i0 + it;
+        if (i < D) {
+            if (is_n) {
+                if (cb == 0) st[(long long)D * DV + i] = S[it];
+            } else if (active) {
+                st[(long long)i * DV + j] = S[it];
+            }
+        }
+    }
     if (MODE == 1) {
-        for (int e = tid; e < D; e += nt) st[D * DV + e] = wv[e];
-        if (tid == 0) st[D * DV + D] = m;
-    } else if (hd == 0 && a.shift_src) {
+        if (cb == 0 && threadIdx.x == 0) st[(long long)D * DV + D] = m;
+    } else if (hd == 0 && cb == 0 && a.shift_src) {
         const T* last = (const T*)a.shift_src + (long long)(s1 - 1) * a.W;
         float* keep = a.state + (long long)a.seq_slot[b] * a.state_stride;
-        for (int e = tid; e < a.W; e += nt) keep[e] = to_f32(last[e]);
+        for (int e = threadIdx.x; e < a.W; e += SCAN_THREADS) keep[e] = to_f32(last[e]);
+    }
+}
+
+// out[t][head] = T(raw / rms(raw over the head's columns) * norm_w * act(g)); act = silu (MODE 0) or sigmoid (MODE 1).
+// One warp per (row, head).  Rows of padding hold whatever `raw` held; nothing reads them.
+template <typename T, int MODE>
+__global__ void __launch_bounds__(128)
+head_norm_gate_kernel(const ScanArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    const long long idx = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (idx >= a.rows * a.H) return;
+    const long long t = idx / a.H;
+    const int hd = (int)(idx - t * a.H), lane = threadIdx.x & 31, DV = a.DV;
+    const float* r = a.raw + t * ((long long)a.H * DV) + (long long)hd * DV;
+    float ss = 0.f;
+    for (int c = lane; c < DV; c += 32) ss = fmaf(r[c], r[c], ss);
+    ss = warp_sum(ss);
+    const float inv = 1.f / sqrtf(ss / (float)DV + a.eps);
+    const T* G = (const T*)a.g + t * a.ldg + (long long)hd * DV;
+    T* O = (T*)a.out + t * a.ldo + (long long)hd * DV;
+    for (int c = lane; c < DV; c += 32) {
+        const float gz = to_f32(G[c]);
+        const float act = MODE == 0 ? gz * sigmoid_f32(gz) : sigmoid_f32(gz);
+        O[c] = from_f32<T>(((r[c] * inv) * a.norm_w[hd * DV + c]) * act);
     }
 }
 
 // mode 0: decay mix, mode 1: matrix memory.  B sequences; rows of the step are found through seq_start.
 extern "C" int cm_matrix_scan(int dt, int mode, const ScanArgs* args, int B, cudaStream_t st) {
     ScanArgs a = *args;
-    if (B <= 0) return CM_OK;
-    if (a.D <= 0 || a.DV <= 0 || a.DV > 1024) CM_REFUSE("matrix_scan: head sizes %d x %d (values up to 1024)", a.D, a.DV);
-    int ks = 256 / a.DV;
-    if (ks < 1) ks = 1;
-    if (ks > a.D) ks = a.D;
+    if (B <= 0 || a.rows <= 0) return CM_OK;
+    if (a.D <= 0 || a.DV <= 0 || a.D > 1024) CM_REFUSE("matrix_scan: head sizes %d x %d (keys up to 1024)", a.D, a.DV);
+    if (!a.raw) CM_REFUSE("matrix_scan: the float buffer for the heads' raw outputs is missing");
+    // Channels per thread (a power of two from 2 to 32) and parts per column (a power of two up to 32: the parts of
+    // a column share a warp): as many channels as leave the grid with about two blocks per SM.
+    auto parts_for = [&](int r) { int k = 1; while (k * r < a.D) k *= 2; return k; };
+    auto blocks = [&](int k) {
+        const int real = SCAN_THREADS / k - (mode == 1 ? 1 : 0);
+        return real < 1 ? 0LL : (long long)a.H * ((a.DV + real - 1) / real) * B;
+    };
+    int rpt = 32;
+    while (rpt > 2 && parts_for(rpt / 2) <= 32 && blocks(parts_for(rpt)) < 2 * 148) rpt /= 2;
+    const int ks = parts_for(rpt);
+    if (ks > 32) CM_REFUSE("matrix_scan: heads of %d key channels (up to 1024)", a.D);
     a.KS = ks;
-    const int threads = (a.DV * ks + 31) / 32 * 32;
-    const size_t smem = ((size_t)a.D * a.DV + 4 * (size_t)a.D + (size_t)ks * a.DV) * sizeof(float);
-    if (smem > 200 * 1024) CM_REFUSE("matrix_scan: a state of %d x %d floats does not fit shared memory", a.D, a.DV);
-    dim3 grid(a.H, B);
-#define SCAN_LAUNCH(TT, M)                                                                                      \
-    do {                                                                                                        \
-        if (smem > 48 * 1024)                                                                                   \
-            cudaFuncSetAttribute(matrix_scan_kernel<TT, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        cm_launch(matrix_scan_kernel<TT, M>, grid, threads, smem, st, a);                                       \
+    const int cols = SCAN_THREADS / ks, real = cols - (mode == 1 ? 1 : 0);
+    const int row_floats = (mode == 0 ? 3 : 2) * ks * rpt + cols + 4 + SCAN_THREADS;
+    int tb = 12288 / row_floats;                          // about 48 KB of staged rows
+    tb = tb < 1 ? 1 : (tb > SCAN_MAX_ROWS ? SCAN_MAX_ROWS : tb);
+    const size_t smem = (size_t)tb * row_floats * sizeof(float);
+    dim3 grid(a.H, (a.DV + real - 1) / real, B);
+    dim3 egrid((unsigned)((a.rows * a.H + 3) / 4));
+#define SCAN_LAUNCH(TT, M, R)                                                                                    \
+    do {                                                                                                         \
+        if (smem > 48 * 1024)                                                                                    \
+            cudaFuncSetAttribute(matrix_scan_kernel<TT, M, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        cm_launch(matrix_scan_kernel<TT, M, R>, grid, SCAN_THREADS, smem, st, a, tb);                                \
     } while (0)
-    if (dt == DT_F32 && mode == 0) SCAN_LAUNCH(float, 0);
-    else if (dt == DT_F32 && mode == 1) SCAN_LAUNCH(float, 1);
-    else if (dt == DT_BF16 && mode == 0) SCAN_LAUNCH(bf16, 0);
-    else if (dt == DT_BF16 && mode == 1) SCAN_LAUNCH(bf16, 1);
+#define SCAN_RPT(TT, M)                             \
+    do {                                            \
+        if (rpt == 2) SCAN_LAUNCH(TT, M, 2);        \
+        else if (rpt == 4) SCAN_LAUNCH(TT, M, 4);   \
+        else if (rpt == 8) SCAN_LAUNCH(TT, M, 8);   \
+        else if (rpt == 16) SCAN_LAUNCH(TT, M, 16); \
+        else SCAN_LAUNCH(TT, M, 32);                \
+    } while (0)
+    if (dt == DT_F32 && mode == 0) { SCAN_RPT(float, 0); CM_CHECK_LAUNCH(); cm_launch(head_norm_gate_kernel<float, 0>, egrid, 128, 0, st, a); }
+    else if (dt == DT_F32 && mode == 1) { SCAN_RPT(float, 1); CM_CHECK_LAUNCH(); cm_launch(head_norm_gate_kernel<float, 1>, egrid, 128, 0, st, a); }
+    else if (dt == DT_BF16 && mode == 0) { SCAN_RPT(bf16, 0); CM_CHECK_LAUNCH(); cm_launch(head_norm_gate_kernel<bf16, 0>, egrid, 128, 0, st, a); }
+    else if (dt == DT_BF16 && mode == 1) { SCAN_RPT(bf16, 1); CM_CHECK_LAUNCH(); cm_launch(head_norm_gate_kernel<bf16, 1>, egrid, 128, 0, st, a); }
     else return CM_ERR_DTYPE;
+#undef SCAN_RPT
 #undef SCAN_LAUNCH
     CM_CHECK_LAUNCH();
     return CM_OK;

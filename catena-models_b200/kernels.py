@@ -776,9 +776,9 @@ def shift_mix(out, h, mu, state, tok_seq, tok_pos, seq_pos0, seq_slot):
 
 
 def lowrank_decay(out, x, w1, w2, w0):
-    """out = exp(-exp(W2 tanh(W1 x) + w0)) in float32: x [rows, W], W1 [R, W], W2 [C, R], w0 [C]."""
+    """out = exp(-exp(W2 tanh(W1 x) + w0)) in float32: x [rows, W], W1 [R, W], w2 = W2 transposed [R, C], w0 [C]."""
     rows, W = x.shape
-    R, C = w1.shape[0], w2.shape[0]
+    R, C = w1.shape[0], w2.shape[1]
     if w1.dtype != x.dtype or w2.dtype != x.dtype or not (x.is_contiguous() and w1.is_contiguous() and w2.is_contiguous()):
         raise KernelError("lowrank_decay: contiguous operands of one dtype")
     _check(lib().cm_lowrank_decay(dtype_code(x.dtype), _ptr(out), _ptr(x), _ptr(w1), _ptr(w2), _ptr(w0), rows, W, R, C,
@@ -802,7 +802,8 @@ class _ScanArgs(ctypes.Structure):
     _fields_ = [("q", _vp), ("k", _vp), ("v", _vp), ("g", _vp), ("ldq", _ll), ("ldk", _ll), ("ldv", _ll), ("ldg", _ll),
                 ("decay", _vp), ("bonus", _vp), ("norm_w", _vp), ("out", _vp), ("ldo", _ll), ("state", _vp),
                 ("state_stride", _ll), ("state_offset", _ll), ("shift_src", _vp), ("W", _i), ("seq_start", _vp),
-                ("seq_slot", _vp), ("H", _i), ("D", _i), ("DV", _i), ("KS", _i), ("q_scale", _f), ("eps", _f)]
+                ("seq_slot", _vp), ("H", _i), ("D", _i), ("DV", _i), ("KS", _i), ("q_scale", _f), ("eps", _f), ("raw", _vp),
+                ("rows", _ll)]
 
 
 def matrix_scan(mode, out, q, k, v, g, decay, bonus, norm_w, state, state_offset, seq_start, seq_slot, B, H, D, DV,
@@ -817,14 +818,15 @@ def matrix_scan(mode, out, q, k, v, g, decay, bonus, norm_w, state, state_offset
     for t in (q, k, v, g, out):
         if t.stride(1) != 1 or t.dtype != out.dtype:
             raise KernelError("matrix_scan: row-major operands of one dtype")
-    a = _ScanArgs(q=_ptr(q), k=_ptr(k), v=_ptr(v), g=_ptr(g), ldq=q.stride(0), ldk=k.stride(0), ldv=v.stride(0),
+    rows = q.shape[0]
+    raw = torch.empty((rows, H * DV), dtype=torch.float32, device=q.device)      # the heads' outputs before norm and gate
+    a = _ScanArgs(raw=_ptr(raw), rows=rows, q=_ptr(q), k=_ptr(k), v=_ptr(v), g=_ptr(g), ldq=q.stride(0), ldk=k.stride(0), ldv=v.stride(0),
                   ldg=g.stride(0), decay=_ptr(decay), bonus=_ptr(bonus), norm_w=_ptr(norm_w), out=_ptr(out),
                   ldo=out.stride(0), state=_ptr(state), state_stride=state.stride(0), state_offset=state_offset,
                   shift_src=_ptr(shift_src), W=0 if shift_src is None else shift_src.shape[1], seq_start=_ptr(seq_start),
                   seq_slot=_ptr(seq_slot), H=H, D=D, DV=DV, KS=0, q_scale=q_scale, eps=eps)
-    rows = q.shape[0]
     _check(lib().cm_matrix_scan(dtype_code(out.dtype), {"decay": 0, "memory": 1}[mode], ctypes.byref(a), B, _stream()),
-           "matrix_scan_" + mode,
+           "matrix_scan_" + mode, 2,
            cost=lambda: (f"{B} sequences, {rows} rows, {H} heads of {D}x{DV}",
                          _nbytes(q, k, v, g, out) + (0 if decay is None else rows * decay.shape[1] * 4) + 2 * B * H * D * DV * 4,
                          6 * rows * H * D * DV))

@@ -35,13 +35,12 @@ from ..weights.loader import TensorSpec
 from .base import Mixer, register_part
 from .linear import Linear
 
-SCAN_SHARED_BYTES = 200 * 1024      # what the scan kernel may hold in shared memory (csrc/recurrent.cu)
+SCAN_MAX_KEY_DIM = 1024             # a column's key channels are spread over the lanes of one warp (csrc/recurrent.cu)
 
 
 def scan_fits(dim, value_dim):
-    """True if a head's state of dim x value_dim floats fits the scan kernel's shared memory."""
-    ks = max(1, min(dim, 256 // max(1, value_dim)))
-    return value_dim <= 1024 and (dim * value_dim + 4 * dim + ks * value_dim) * 4 <= SCAN_SHARED_BYTES
+    """True if the scan kernel takes heads of dim key channels (any number of value channels)."""
+    return 1 <= dim <= SCAN_MAX_KEY_DIM and value_dim >= 1
 
 
 class DecayMix(Mixer):
@@ -70,7 +69,7 @@ class DecayMix(Mixer):
         p = self.prefix
         f32 = lambda name: tensors[p + name].to(torch.float32).contiguous()
         self.mu = torch.stack([f32("mu." + s) for s in "rkvgw"]).contiguous()
-        self.w1, self.w2 = tensors[p + "w1"].contiguous(), tensors[p + "w2"].contiguous()
+        self.w1, self.w2 = tensors[p + "w1"].contiguous(), tensors[p + "w2"].t().contiguous()     # W2 as [rank, channels]
         self.w0, self.u, self.norm_w = f32("w0"), f32("u"), f32("norm")
         self._bound = [self.mu, self.w1, self.w2, self.w0, self.u, self.norm_w]
 

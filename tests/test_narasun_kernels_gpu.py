@@ -191,7 +191,7 @@ def test_token_shift_decay_network_and_gates():
     close(out, h.double()[None] + (prev.double() - h.double())[None] * mu.double()[:, None], 1e-6)
     w1, w2, w0 = rnd(R, W, seed=32, std=0.3), rnd(C, R, seed=33), rnd(C, seed=34)
     dec = torch.empty((T, C), device=DEV)
-    kernels.lowrank_decay(dec, h, w1, w2, w0)
+    kernels.lowrank_decay(dec, h, w1, w2.t().contiguous(), w0)
     close(dec, torch.exp(-torch.exp(torch.tanh(h.double() @ w1.double().T) @ w2.double().T + w0.double())), 1e-5)
     wg, bias, cap = rnd(2 * H, W, seed=35), rnd(2 * H, seed=36), 4.0
     gates = torch.empty((T, 2 * H), device=DEV)
