@@ -89,7 +89,10 @@ template <int BLOCK_N, int STAGES, typename TC, int MODE>
 __global__ void __launch_bounds__(TCP_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_c, int tma_store_ok, TC* __restrict__ C, int M, int N, int K,
-               long long ldc, int ksplit, long long part_stride, int* err) {
+               long long ldc, int ksplit, long long part_stride, int* err, const int* __restrict__ tile_group,
+               int group_rows) {
+    // tile_group (or null): B is a stack of matrices of group_rows rows each, and the 128 rows of row tile t are
+    // multiplied by matrix tile_group[t] (a grouped product: the rows of a routed feed-forward, sorted by expert)
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
     constexpr uint32_t B_BYTES = BLOCK_N * TC_BK * 2;
     constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
@@ -148,6 +151,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             int m_tile, n_tile;
             tile_origin(tile, m_tiles, n_tiles, &m_tile, &n_tile);
             const int m0 = m_tile * TC_BM, n0 = n_tile * OUT_COLS;
+            const int b0 = n0 + (tile_group ? tile_group[m_tile] * group_rows : 0);       // first row of B for this tile
             const int kb_end = min(num_kb, (run + 1) * kb_per);
             for (int kb = run * kb_per; kb < kb_end; ++kb, ++it) {
                 const int s = it % STAGES;
@@ -158,10 +162,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
                 tma_load_2d(a_dst, &map_a, full0 + 8 * s, kb * TC_BK, m0);
                 if (MODE == TC_MODE_SWIGLU) {
-                    tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * TC_BK, n0);
-                    tma_load_2d(b_dst + B_BYTES / 2, &map_b, full0 + 8 * s, kb * TC_BK, N + n0);
+                    tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * TC_BK, b0);
+                    tma_load_2d(b_dst + B_BYTES / 2, &map_b, full0 + 8 * s, kb * TC_BK, N + b0);
                 } else {
-                    tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * TC_BK, n0);
+                    tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * TC_BK, b0);
                 }
                 issued_kb = it + 1;
             }
@@ -583,9 +587,11 @@ static int make_map_c(CUtensorMap* map, void* base, long long M, long long N, lo
 
 template <int BLOCK_N, int STAGES, typename TC, int MODE>
 static int launch_tc(void* C, const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
-                     long long ldc, int* err, cudaStream_t st, int ksplit = 1, long long part_stride = 0) {
+                     long long ldc, int* err, cudaStream_t st, int ksplit = 1, long long part_stride = 0,
+                     const int* tile_group = nullptr, int groups = 1) {
     CUtensorMap map_a, map_b;
-    const long long b_rows = MODE == TC_MODE_SWIGLU ? 2LL * N : N;
+    const int group_rows = MODE == TC_MODE_SWIGLU ? 2 * N : N;
+    const long long b_rows = (long long)groups * group_rows;
     const int b_box = MODE == TC_MODE_SWIGLU ? BLOCK_N / 2 : BLOCK_N;
     int rc = make_map(&map_a, A, M, K, lda, TC_BM);
     if (rc != CM_OK) return rc;
@@ -622,7 +628,7 @@ static int launch_tc(void* C, const void* A, const void* B, int M, int N, int K,
     const int num_items = num_tiles * ksplit;
     dim3 grid(num_items < sm_count ? num_items : sm_count);
     cm_launch(kernel, grid, TCP_THREADS, smem, st, map_a, map_b, map_c, tma_store, (TC*)C, M, N, K, ldc, ksplit,
-              part_stride, err);
+              part_stride, err, tile_group, group_rows);
     CM_CHECK_LAUNCH();
     return CM_OK;
 }
@@ -744,6 +750,32 @@ extern "C" int cm_gemm_tc(int dtc, void* C, const void* A, const void* B, int M,
         return launch_tc<192, 4, bf16, TC_MODE_PLAIN>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
     if (dtc == DT_BF16) return launch_tc<128, 6, bf16, TC_MODE_PLAIN>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
     if (dtc == DT_F32) return launch_tc<128, 6, float, TC_MODE_PLAIN>(C, A, B, M, N, K, lda, ldb, ldc, err, st);
+    return CM_ERR_DTYPE;
+}
+
+// The grouped form: B is `groups` matrices of N rows (2N when swiglu) one below the other, and the rows of row tile t
+// (128 rows) are multiplied by matrix tile_group[t] (device int32, one entry per row tile of A).  Everything else as
+// cm_gemm_tc; C bfloat16, or float for the plain product.
+extern "C" int cm_gemm_tc_grouped(int dtc, void* C, const void* A, const void* B, int M, int N, int K, long long lda,
+                                  long long ldb, long long ldc, int swiglu, int block_n, const int* tile_group, int groups,
+                                  int* err, cudaStream_t st) {
+    if (M <= 0 || N <= 0) return CM_OK;
+    if (K <= 0 || K % 8 || lda % 8 || ldb % 8)
+        CM_REFUSE("gemm_tc_grouped: inner size %d and row pitches %lld, %lld must be multiples of 8", K, lda, ldb);
+    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15)
+        CM_REFUSE("gemm_tc_grouped: operands must be 16-byte aligned");
+    if (!tile_group || groups < 1) CM_REFUSE("gemm_tc_grouped: the row tiles' groups are missing");
+    if (block_n != 128 && block_n != 256) CM_REFUSE("gemm_tc_grouped: tile width %d (128 or 256)", block_n);
+    if (swiglu) {
+        if (dtc != DT_BF16) return CM_ERR_DTYPE;
+        if (block_n == 256)
+            return launch_tc<256, 4, bf16, TC_MODE_SWIGLU>(C, A, B, M, N, K, lda, ldb, ldc, err, st, 1, 0, tile_group, groups);
+        return launch_tc<128, 6, bf16, TC_MODE_SWIGLU>(C, A, B, M, N, K, lda, ldb, ldc, err, st, 1, 0, tile_group, groups);
+    }
+    if (dtc == DT_BF16 && block_n == 256)
+        return launch_tc<256, 4, bf16, TC_MODE_PLAIN>(C, A, B, M, N, K, lda, ldb, ldc, err, st, 1, 0, tile_group, groups);
+    if (dtc == DT_BF16) return launch_tc<128, 6, bf16, TC_MODE_PLAIN>(C, A, B, M, N, K, lda, ldb, ldc, err, st, 1, 0, tile_group, groups);
+    if (dtc == DT_F32) return launch_tc<128, 6, float, TC_MODE_PLAIN>(C, A, B, M, N, K, lda, ldb, ldc, err, st, 1, 0, tile_group, groups);
     return CM_ERR_DTYPE;
 }
 

@@ -10,8 +10,8 @@
 //               optionally divided by their sum
 //   experts     a = act(W_gate x) * (W_up x), y = W_down a, with x = weight * h (the weight on the
 //               expert's INPUT) or x = h and y = weight * y (the weight on its output)
-//   result      one row of y per pair, float, pair p = token * top + choice: the consumer adds a token's
-//               rows in the order of the choices.
+//   result      one row of y per pair, float, in the order of the experts; dest[token * top + choice] says
+//               where a pair's row is, and the consumer adds a token's rows in the order of its choices.
 //
 // A pair's result does not depend on which tile it lands in (every output is one dot product in a fixed
 // order), so the order of the pairs inside an expert, which comes from atomic counters, changes nothing.
@@ -76,44 +76,93 @@ moe_router_kernel(int* __restrict__ ids, float* __restrict__ wts, int* __restric
         for (int j = 0; j < top; ++j) wts[t * top + j] /= total;
 }
 
-// One block, one thread's walk over the experts: where each expert's rows begin, and the list of row
-// tiles.  plan: [0] number of tiles, then per tile (expert, first row, rows).  cursor[e] = offset[e].
-__global__ void moe_plan_kernel(const int* __restrict__ counts, int* __restrict__ cursor, int* __restrict__ plan, int E) {
+// One block, one thread's walk over the experts: where each expert's rows begin (a multiple of tile_rows: an
+// expert's rows fill whole row tiles, the last one partly), and the list of row tiles.  plan: [0] number of
+// tiles, then per tile (expert, first row, rows); tile_group[t]: the expert of row tile t (0 for tiles that no
+// expert uses).  cursor[e] = the first row of expert e.
+__global__ void moe_plan_kernel(const int* __restrict__ counts, int* __restrict__ cursor, int* __restrict__ plan,
+                                int* __restrict__ tile_group, int E, int tile_rows, int max_tiles) {
     pdl_trigger();
     pdl_wait();
     if (threadIdx.x != 0) return;
-    int off = 0, n = 0;
+    int n = 0;
     for (int e = 0; e < E; ++e) {
         const int c = counts[e];
-        cursor[e] = off;
-        for (int r = 0; r < c; r += MOE_TM) {
+        cursor[e] = n * tile_rows;
+        for (int r = 0; r < c; r += tile_rows) {
             plan[1 + 3 * n] = e;
-            plan[2 + 3 * n] = off + r;
-            plan[3 + 3 * n] = min(MOE_TM, c - r);
+            plan[2 + 3 * n] = n * tile_rows;
+            plan[3 + 3 * n] = min(tile_rows, c - r);
+            tile_group[n] = e;
             ++n;
         }
-        off += c;
     }
     plan[0] = n;
+    for (; n < max_tiles; ++n) tile_group[n] = 0;
 }
 
-__global__ void moe_scatter_kernel(int* __restrict__ perm, int* __restrict__ cursor, const int* __restrict__ ids, long long P) {
+// perm[sorted row] = pair, dest[pair] = sorted row (-1 for pairs of padding rows).
+__global__ void moe_scatter_kernel(int* __restrict__ perm, int* __restrict__ dest, int* __restrict__ cursor,
+                                   const int* __restrict__ ids, long long P) {
     pdl_trigger();
     pdl_wait();
     const long long p = blockIdx.x * (long long)blockDim.x + threadIdx.x;
     if (p >= P) return;
     const int e = ids[p];
-    if (e >= 0) perm[atomicAdd(cursor + e, 1)] = (int)p;
+    int pos = -1;
+    if (e >= 0) {
+        pos = atomicAdd(cursor + e, 1);
+        perm[pos] = (int)p;
+    }
+    dest[p] = pos;
 }
 
-// work: int32 scratch of E (counts) + E (cursor) + 1 + 3 * max_tiles (plan) entries; perm: P entries.
-extern "C" int cm_moe_route(int dt, int* ids, float* wts, int* perm, int* work, const void* h, const void* wr,
+// xs[dest[p]] = T(h[p / top] * (apply_weight ? wts[p] : 1)): the experts' inputs in the order of the experts.
+template <typename T>
+__global__ void moe_gather_kernel(T* __restrict__ xs, const T* __restrict__ h, const int* __restrict__ dest,
+                                  const float* __restrict__ wts, int top, int K, int apply_weight) {
+    pdl_trigger();
+    pdl_wait();
+    const long long p = blockIdx.x;
+    const int d = dest[p];
+    if (d < 0) return;
+    const float w = apply_weight ? wts[p] : 1.f;
+    const T* src = h + (p / top) * K;
+    T* dst = xs + (long long)d * K;
+    for (int c = threadIdx.x; c < K; c += blockDim.x) dst[c] = from_f32<T>(to_f32(src[c]) * w);
+}
+
+extern "C" int cm_moe_gather(int dt, void* xs, const void* h, const int* dest, const float* wts, long long pairs,
+                             int top, int K, int apply_weight, cudaStream_t st) {
+    if (pairs <= 0) return CM_OK;
+    if (dt == DT_F32)
+        cm_launch(moe_gather_kernel<float>, (unsigned)pairs, 128, 0, st, (float*)xs, (const float*)h, dest, wts, top, K, apply_weight);
+    else if (dt == DT_BF16)
+        cm_launch(moe_gather_kernel<bf16>, (unsigned)pairs, 128, 0, st, (bf16*)xs, (const bf16*)h, dest, wts, top, K, apply_weight);
+    else
+        return CM_ERR_DTYPE;
+    CM_CHECK_LAUNCH();
+    return CM_OK;
+}
+
+// Row tiles that `pairs` rows of `E` experts can need at most, each expert's rows starting a tile of its own.
+static int max_tiles_for(long long pairs, int E, int tile_rows) {
+    const long long full = (pairs + tile_rows - 1) / tile_rows;
+    return (int)(full + (pairs < E ? pairs : E));
+}
+
+// work: int32 scratch of E (counts) + E (cursor) + 1 + 3 * max_tiles (plan) + max_tiles (tile_group) entries;
+// perm: max_tiles * tile_rows entries (sorted rows), dest: P entries.  tile_rows: 32 for the CUDA-core grouped
+// products of this file, 128 for the tensor-core grouped product.
+extern "C" int cm_moe_route(int dt, int* ids, float* wts, int* perm, int* dest, int* work, const void* h, const void* wr,
                             const int* tok_seq, long long rows, int W, int E, int top, int softmax_gate,
-                            int renormalize, cudaStream_t st) {
+                            int renormalize, int tile_rows, cudaStream_t st) {
     if (rows <= 0) return CM_OK;
     if (top < 1 || top > E) CM_REFUSE("moe_route: %d of %d experts", top, E);
     if ((size_t)E * sizeof(float) > 48 * 1024) CM_REFUSE("moe_route: %d experts", E);
-    int *counts = work, *cursor = work + E, *plan = work + 2 * E;
+    if (tile_rows != MOE_TM && tile_rows != 128) CM_REFUSE("moe_route: row tiles of %d (32 or 128)", tile_rows);
+    const int max_tiles = max_tiles_for(rows * top, E, tile_rows);
+    int *counts = work, *cursor = work + E, *plan = work + 2 * E, *tile_group = plan + 1 + 3 * max_tiles;
     if (cudaMemsetAsync(counts, 0, (size_t)E * sizeof(int), st) != cudaSuccess) {
         cm_set_error("moe_route: memset failed");
         return CM_ERR_LAUNCH;
@@ -128,24 +177,21 @@ extern "C" int cm_moe_route(int dt, int* ids, float* wts, int* perm, int* work, 
     else
         return CM_ERR_DTYPE;
     CM_CHECK_LAUNCH();
-    cm_launch(moe_plan_kernel, 1, 32, 0, st, counts, cursor, plan, E);
+    cm_launch(moe_plan_kernel, 1, 32, 0, st, counts, cursor, plan, tile_group, E, tile_rows, max_tiles);
     CM_CHECK_LAUNCH();
     const long long P = rows * top;
-    cm_launch(moe_scatter_kernel, (unsigned)((P + 255) / 256), 256, 0, st, perm, cursor, ids, P);
+    cm_launch(moe_scatter_kernel, (unsigned)((P + 255) / 256), 256, 0, st, perm, dest, cursor, ids, P);
     CM_CHECK_LAUNCH();
     return CM_OK;
 }
 
-extern "C" int cm_moe_max_tiles(long long pairs, int E) {
-    const long long full = (pairs + MOE_TM - 1) / MOE_TM;
-    return (int)(full + (pairs < E ? pairs : E));
-}
+extern "C" int cm_moe_max_tiles(long long pairs, int E, int tile_rows) { return max_tiles_for(pairs, E, tile_rows); }
 
 // ------------------------------------------------------------------------------ grouped products
 // UP:   a[row] = act(Wg_e x) * (Wu_e x) for the sorted rows of a tile; x = h[token of the pair] (times the
 //       pair's weight when scale_input); w: [E][2 F][K] (gate rows, then up rows); out a: [P][F], sorted order.
-// DOWN: y[pair] = Wd_e a[row] (times the pair's weight when scale_output); w: [E][N][K]; out y: [P][N] float,
-//       by pair.
+// DOWN: y[row] = Wd_e a[row] (times the pair's weight when scale_output); w: [E][N][K]; out y: [rows][N] float,
+//       sorted order as well (dest[pair] says where a pair's row is).
 // A block computes MOE_TM rows x MOE_TN columns; a thread 4 rows x 2 columns (and both halves for UP).
 template <typename T, bool UP>
 __global__ void __launch_bounds__(MOE_THREADS)
@@ -225,10 +271,9 @@ moe_grouped_kernel(void* __restrict__ out, const T* __restrict__ x, const T* __r
                 else act = g * sigmoid_f32(g);
                 reinterpret_cast<T*>(out)[(long long)(row0 + r) * N + n] = from_f32<T>(act * u);
             } else {
-                const int p = perm[row0 + r];
                 float y = acc[0][i][c];
                 if (apply_weight) y *= row_w[r];
-                reinterpret_cast<float*>(out)[(long long)p * N + n] = y;
+                reinterpret_cast<float*>(out)[(long long)(row0 + r) * N + n] = y;
             }
         }
     }

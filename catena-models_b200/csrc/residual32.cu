@@ -14,6 +14,7 @@
 // one piece per chosen expert), stored as float or as activations, times a constant.
 struct ResidualTerm {
     const void* p;
+    const int* index;      // null: piece j of row r is row r * per_row + j; else row index[r * per_row + j] (negative: none)
     float scale;
     int per_row;
     int is_f32;
@@ -67,7 +68,10 @@ residual_add_norm_kernel(float* __restrict__ h, T* __restrict__ n_out, ResidualT
         for (int i = 0; i < terms.n; ++i) {
             const ResidualTerm& t = terms.t[i];
             float s = 0.f;
-            for (int j = 0; j < t.per_row; ++j) s += term_at<T>(t, (r * t.per_row + j) * H + c);
+            for (int j = 0; j < t.per_row; ++j) {
+                const long long piece = t.index ? t.index[r * t.per_row + j] : r * t.per_row + j;
+                if (piece >= 0) s += term_at<T>(t, piece * H + c);
+            }
             add += t.scale * s;
         }
         float v = hr[c] + add;
@@ -120,10 +124,10 @@ extern "C" int cm_norm_f32in(int dt, void* y, const float* x, const float* w, in
     return CM_OK;
 }
 
-// terms: n_terms entries of (pointer, scale, pieces per row, stored as float?) in four parallel arrays.
+// terms: n_terms entries of (pointer, scale, pieces per row, stored as float?, index of the pieces or null) in parallel arrays.
 extern "C" int cm_residual_add_norm(int dt, float* h, void* n_out, int n_terms, const void* const* term_ptr,
                                     const float* term_scale, const int* term_per_row, const int* term_is_f32,
-                                    const float* bias, const float* w, int rows, int H, float eps, cudaStream_t st) {
+                                    const int* const* term_index, const float* bias, const float* w, int rows, int H, float eps, cudaStream_t st) {
     if (rows <= 0) return CM_OK;
     if (n_terms < 0 || n_terms > R32_MAX_TERMS) CM_REFUSE("residual_add_norm: %d terms (at most %d)", n_terms, R32_MAX_TERMS);
     if (n_out && !w) CM_REFUSE("residual_add_norm: a norm needs its weight");
@@ -133,6 +137,7 @@ extern "C" int cm_residual_add_norm(int dt, float* h, void* n_out, int n_terms, 
     terms.n = n_terms;
     for (int i = 0; i < R32_MAX_TERMS; ++i) {
         terms.t[i].p = i < n_terms ? term_ptr[i] : nullptr;
+        terms.t[i].index = i < n_terms ? term_index[i] : nullptr;
         terms.t[i].scale = i < n_terms ? term_scale[i] : 0.f;
         terms.t[i].per_row = i < n_terms ? term_per_row[i] : 0;
         terms.t[i].is_f32 = i < n_terms ? term_is_f32[i] : 0;

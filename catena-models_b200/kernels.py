@@ -54,13 +54,15 @@ _SIGNATURES = {
     "cm_zero_slots": [_vp, _i, _ll, _ll, ctypes.POINTER(ctypes.c_int), _i, _vp],
     "cm_copy_pages": [_vp, _vp, _vp, _i, _i, _ll, _ll, _vp],
     "cm_norm_f32in": [_i, _vp, _vp, _vp, _i, _i, _f, _vp],
-    "cm_residual_add_norm": [_i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp],
+    "cm_residual_add_norm": [_i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp],
     "cm_concat_cast": [_i, _vp, _vp, _vp, _ll, _i, _vp],
     "cm_shift_mix": [_i, _vp, _vp, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _i, _ll, _i, _vp],
     "cm_lowrank_decay": [_i, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _vp],
     "cm_capped_gates": [_i, _vp, _vp, _vp, _vp, _f, _ll, _i, _i, _vp],
     "cm_matrix_scan": [_i, _i, _vp, _i, _vp],
-    "cm_moe_route": [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _vp],
+    "cm_moe_route": [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _i, _vp],
+    "cm_moe_gather": [_i, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _vp],
+    "cm_gemm_tc_grouped": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _vp, _i, _vp, _vp],
     "cm_moe_grouped": [_i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
 }
 
@@ -343,8 +345,9 @@ class PartialSums:
 
 
 class Terms(list):
-    """What a sublayer adds to a float32 residual stream: (tensor, factor, pieces per row) entries; the
-    tensor holds rows * pieces rows, float32 or in the activation dtype (`residual_add_norm`)."""
+    """What a sublayer adds to a float32 residual stream: (tensor, factor, pieces per row[, index]) entries; the
+    tensor holds a row's pieces one below the other (rows * pieces rows), or anywhere, with `index` (int32
+    [rows * pieces], negative: no piece) saying where; float32 or the activation dtype (`residual_add_norm`)."""
 
 
 def add_norm(h_out, n_out, m, h_in, w_post, w_next, eps_post, eps_next):
@@ -740,22 +743,26 @@ def norm_f32in(out, x, w, eps):
 def residual_add_norm(h, terms, n_out=None, w_next=None, eps=0.0, bias=None):
     """h (float32, in place) += sum over `terms` of scale * (the sum of a row's pieces) (+ bias, a float32
     row); n_out = norm(h) * w_next in the activation dtype when given.  A term is (tensor, scale, pieces
-    per row): the tensor holds rows * pieces rows of h's width, float32 or the activation dtype."""
+    per row) or (tensor, scale, pieces per row, index): see `Terms`."""
     rows, H = h.shape
     if h.dtype != torch.float32 or not h.is_contiguous() or len(terms) > 4:
         raise KernelError("residual_add_norm: a contiguous float32 stream and at most four terms")
-    act = n_out.dtype if n_out is not None else next((t.dtype for t, _, _ in terms if t.dtype != torch.float32), torch.float32)
-    for t, _, per_row in terms:
-        if not t.is_contiguous() or t.numel() != rows * per_row * H or t.dtype not in (torch.float32, act):
+    terms = [tuple(t) + (None,) * (4 - len(t)) for t in terms]
+    act = n_out.dtype if n_out is not None else next((t[0].dtype for t in terms if t[0].dtype != torch.float32), torch.float32)
+    for t, _, per_row, index in terms:
+        fits = t.numel() == rows * per_row * H if index is None else (index.numel() == rows * per_row and t.shape[-1] == H)
+        if not t.is_contiguous() or not fits or t.dtype not in (torch.float32, act):
             raise KernelError("residual_add_norm: a term's shape or dtype does not fit")
     n = len(terms)
-    ptrs = (ctypes.c_void_p * 4)(*[t.data_ptr() for t, _, _ in terms], *([None] * (4 - n)))
-    scales = (ctypes.c_float * 4)(*[float(s) for _, s, _ in terms], *([0.0] * (4 - n)))
-    per = (ctypes.c_int * 4)(*[int(p) for _, _, p in terms], *([0] * (4 - n)))
-    f32 = (ctypes.c_int * 4)(*[int(t.dtype == torch.float32) for t, _, _ in terms], *([0] * (4 - n)))
-    _check(lib().cm_residual_add_norm(dtype_code(act), _ptr(h), _ptr(n_out), n, ptrs, scales, per, f32, _ptr(bias),
+    ptrs = (ctypes.c_void_p * 4)(*[t[0].data_ptr() for t in terms], *([None] * (4 - n)))
+    scales = (ctypes.c_float * 4)(*[float(t[1]) for t in terms], *([0.0] * (4 - n)))
+    per = (ctypes.c_int * 4)(*[int(t[2]) for t in terms], *([0] * (4 - n)))
+    f32 = (ctypes.c_int * 4)(*[int(t[0].dtype == torch.float32) for t in terms], *([0] * (4 - n)))
+    index = (ctypes.c_void_p * 4)(*[_ptr(t[3]) for t in terms], *([None] * (4 - n)))
+    _check(lib().cm_residual_add_norm(dtype_code(act), _ptr(h), _ptr(n_out), n, ptrs, scales, per, f32, index, _ptr(bias),
                                       _ptr(w_next), rows, H, eps, _stream()), "residual_add_norm",
-           cost=lambda: (f"{rows}x{H}, {n} terms", 2 * _nbytes(h) + _nbytes(n_out, *[t for t, _, _ in terms]), (n + 5) * rows * H))
+           cost=lambda: (f"{rows}x{H}, {n} terms", 2 * _nbytes(h) + _nbytes(n_out) + sum(rows * t[2] * H * t[0].element_size() for t in terms),
+                         (n + 5) * rows * H))
 
 
 def concat_cast(out, a, b):
@@ -833,29 +840,53 @@ def matrix_scan(mode, out, q, k, v, g, decay, bonus, norm_w, state, state_offset
 
 
 # ------------------------------------------------------------------ routed feed-forward
-def moe_max_tiles(pairs, experts):
+MOE_TILE_SIMT, MOE_TILE_TC = 32, 128     # rows of a row tile: the CUDA-core grouped products, the tcgen05 grouped product
+
+
+def moe_max_tiles(pairs, experts, tile_rows=MOE_TILE_SIMT):
     fn = lib().cm_moe_max_tiles
-    fn.argtypes, fn.restype = [_ll, _i], _i
-    return fn(pairs, experts)
+    fn.argtypes, fn.restype = [_ll, _i, _i], _i
+    return fn(pairs, experts, tile_rows)
 
 
-def moe_route(ids, wts, perm, work, h, w_router, tok_seq, top, softmax_gate=False, renormalize=False):
+def moe_work_size(pairs, experts, tile_rows=MOE_TILE_SIMT):
+    """int32 entries of `moe_route`'s scratch: counts, cursors, the list of row tiles, each row tile's expert."""
+    return 2 * experts + 1 + 4 * moe_max_tiles(pairs, experts, tile_rows)
+
+
+def moe_tile_group(work, pairs, experts, tile_rows):
+    """The part of `work` that holds each row tile's expert (what the grouped tcgen05 product reads)."""
+    tiles = moe_max_tiles(pairs, experts, tile_rows)
+    return work[2 * experts + 1 + 3 * tiles:2 * experts + 1 + 4 * tiles]
+
+
+def moe_route(ids, wts, perm, dest, work, h, w_router, tok_seq, top, softmax_gate=False, renormalize=False,
+              tile_rows=MOE_TILE_SIMT):
     """Scores of every token's experts in float32 (sigmoid, or softmax over the experts), the `top` best
-    (ids, wts: [rows * top]; -1 for rows of padding), and the pairs in the order of their experts (perm)
-    with the list of row tiles in `work` (int32, 2 E + 1 + 3 * moe_max_tiles entries)."""
+    (ids, wts: [rows * top]; -1 for rows of padding), and the pairs in the order of their experts, every expert's
+    rows beginning a row tile of `tile_rows` rows: perm[sorted row] = pair (moe_max_tiles * tile_rows entries),
+    dest[pair] = sorted row (-1: none), the list of row tiles in `work` (int32, moe_work_size entries)."""
     rows, W = h.shape
     E = w_router.shape[0]
     if w_router.dtype != h.dtype or not (h.is_contiguous() and w_router.is_contiguous()):
         raise KernelError("moe_route: contiguous operands of one dtype")
-    _check(lib().cm_moe_route(dtype_code(h.dtype), _ptr(ids), _ptr(wts), _ptr(perm), _ptr(work), _ptr(h), _ptr(w_router),
-                              _ptr(tok_seq), rows, W, E, top, int(softmax_gate), int(renormalize), _stream()), "moe_route", 3,
+    _check(lib().cm_moe_route(dtype_code(h.dtype), _ptr(ids), _ptr(wts), _ptr(perm), _ptr(dest), _ptr(work), _ptr(h),
+                              _ptr(w_router), _ptr(tok_seq), rows, W, E, top, int(softmax_gate), int(renormalize), tile_rows,
+                              _stream()), "moe_route", 3,
            cost=lambda: (f"{rows}x{W} over {E}, top {top}", _nbytes(h, w_router), 2 * rows * E * W))
 
 
+def moe_gather(xs, h, dest, wts, top, apply_weight):
+    """xs[dest[p]] = h[p // top] (times wts[p] if apply_weight): the experts' inputs in the order of the experts."""
+    pairs, K = dest.numel(), h.shape[1]
+    _check(lib().cm_moe_gather(dtype_code(h.dtype), _ptr(xs), _ptr(h), _ptr(dest), _ptr(wts), pairs, top, K, int(apply_weight),
+                               _stream()), "moe_gather", cost=lambda: (f"{pairs}x{K}", 2 * pairs * K * h.element_size(), pairs * K))
+
+
 def moe_grouped(out, x, w, work, perm, wts, top, max_tiles, up, apply_weight, gelu=False):
-    """The experts' products over the rows that `moe_route` gave them.  up: out[sorted row] = act(Wg x) * (Wu x)
-    with x = h[token] (times the pair's weight if apply_weight), w [E, 2 F, K]; else out[pair] (float32) = Wd a
-    (times the weight if apply_weight), w [E, N, K]."""
+    """The experts' products over the rows that `moe_route` gave them (row tiles of 32), on the CUDA cores.
+    up: out[sorted row] = act(Wg x) * (Wu x) with x = h[token] (times the pair's weight if apply_weight), w [E, 2 F, K];
+    else out[sorted row] (float32) = Wd a (times the weight if apply_weight), w [E, N, K]."""
     E = w.shape[0]
     N = w.shape[1] // 2 if up else w.shape[1]
     K = w.shape[2]
@@ -866,3 +897,19 @@ def moe_grouped(out, x, w, work, perm, wts, top, max_tiles, up, apply_weight, ge
            "moe_grouped_" + ("up" if up else "down"),
            cost=lambda: (f"{out.shape[0]} rows, {w.shape[1]}x{K} per expert", _nbytes(x, out) + min(E, out.shape[0]) * w[0].numel() * w.element_size(),
                          2 * out.shape[0] * w.shape[1] * K))
+
+
+def gemm_tc_grouped(y, x, w, tile_group, swiglu=False, err=None, block_n=256):
+    """`gemm_tc` with a matrix per row tile: w [groups, N (2 N when swiglu), K] bfloat16, tile_group (device int32)
+    names the matrix that multiplies each tile of 128 rows of x.  y bfloat16, or float32 for the plain product."""
+    M, K = x.shape
+    G, N = w.shape[0], y.shape[1]
+    if w.shape[2] != K or w.shape[1] != (2 * N if swiglu else N) or y.shape[0] != M or tile_group.numel() * 128 < M:
+        raise KernelError(f"gemm_tc_grouped shapes: x {tuple(x.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)}")
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not (x.is_contiguous() and w.is_contiguous() and y.is_contiguous()):
+        raise KernelError("gemm_tc_grouped takes contiguous bfloat16 operands")
+    _check(lib().cm_gemm_tc_grouped(dtype_code(y.dtype), _ptr(y), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(1), y.stride(0),
+                                    int(swiglu), block_n, _ptr(tile_group), G, _ptr(err), _stream()),
+           "gemm_tc_grouped" + ("_swiglu" if swiglu else ""),
+           cost=lambda: (f"{M}x{w.shape[1]}x{K} over {G} matrices", _nbytes(x, y) + min(G, -(-M // 128)) * w[0].numel() * 2,
+                         2 * M * w.shape[1] * K))

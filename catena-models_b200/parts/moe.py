@@ -69,19 +69,34 @@ class RoutedSwiGLU(FeedForward):
         dev = x.device
         if x.dtype != self.w_up.dtype:
             raise ValueError("RoutedSwiGLU: activations and expert matrices must share a dtype")
-        max_tiles = kernels.moe_max_tiles(P, E)
+        # bfloat16 with rows that TMA can fetch: the grouped tcgen05 product over row tiles of 128; else the CUDA cores
+        tensor_cores = (x.dtype == torch.bfloat16 and not self.gelu and self.hidden % 8 == 0 and self.intermediate % 8 == 0
+                        and self.weight_on_input and (rt.tensor_core_prompts or batch.kind == "decode")
+                        and getattr(rt, "grouped_tensor_cores", True))
+        tile = kernels.MOE_TILE_TC if tensor_cores else kernels.MOE_TILE_SIMT
+        max_tiles = kernels.moe_max_tiles(P, E, tile)
+        rows = max_tiles * tile
         ids = torch.empty(P, dtype=torch.int32, device=dev)
         wts = torch.empty(P, dtype=torch.float32, device=dev)
-        perm = torch.empty(P, dtype=torch.int32, device=dev)
-        work = torch.empty(2 * E + 1 + 3 * max_tiles, dtype=torch.int32, device=dev)
-        kernels.moe_route(ids, wts, perm, work, x, self.router, batch.tok_seq, top, self.softmax_gate, self.renormalize)
-        a = torch.empty((P, self.intermediate), dtype=x.dtype, device=dev)
-        kernels.moe_grouped(a, x, self.w_up, work, perm, wts, top, max_tiles, up=True,
-                            apply_weight=self.weight_on_input, gelu=self.gelu)
-        y = torch.empty((P, self.hidden), dtype=torch.float32, device=dev)
-        kernels.moe_grouped(y, a, self.w_down, work, perm, wts, top, max_tiles, up=False,
-                            apply_weight=not self.weight_on_input)
-        return kernels.Terms([(y, 1.0, top)])
+        perm = torch.empty(rows, dtype=torch.int32, device=dev)
+        dest = torch.empty(P, dtype=torch.int32, device=dev)
+        work = torch.empty(kernels.moe_work_size(P, E, tile), dtype=torch.int32, device=dev)
+        kernels.moe_route(ids, wts, perm, dest, work, x, self.router, batch.tok_seq, top, self.softmax_gate, self.renormalize, tile)
+        a = torch.empty((rows, self.intermediate), dtype=x.dtype, device=dev)
+        y = torch.empty((rows, self.hidden), dtype=torch.float32, device=dev)
+        if tensor_cores:
+            groups = kernels.moe_tile_group(work, P, E, tile)
+            xs = torch.empty((rows, self.hidden), dtype=x.dtype, device=dev)
+            kernels.moe_gather(xs, x, dest, wts, top, self.weight_on_input)
+            kernels.gemm_tc_grouped(a, xs, self.w_up, groups, swiglu=True, err=rt.error_flag,
+                                    block_n=rt._tile_width(rows, 2 * self.intermediate, widths=(256, 128)))
+            kernels.gemm_tc_grouped(y, a, self.w_down, groups, err=rt.error_flag, block_n=128)
+        else:
+            kernels.moe_grouped(a, x, self.w_up, work, perm, wts, top, max_tiles, up=True,
+                                apply_weight=self.weight_on_input, gelu=self.gelu)
+            kernels.moe_grouped(y, a, self.w_down, work, perm, wts, top, max_tiles, up=False,
+                                apply_weight=not self.weight_on_input)
+        return kernels.Terms([(y, 1.0, top, dest)])
 
 
 register_part("feed_forward", "routed_swiglu", RoutedSwiGLU)

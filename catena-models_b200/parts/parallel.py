@@ -49,7 +49,7 @@ class SideBySide(Mixer):
         for i, (mixer, scale) in enumerate(((self.a, self.a_scale), (self.b, self.b_scale))):
             view = state.views[i]
             view.owned, view.unit = state.owned, (state.unit, i)
-            out += [(t, s * scale, n) for t, s, n in _terms(mixer.forward(rt, batch, x, view))]
+            out += [(e[0], e[1] * scale, *e[2:]) for e in _terms(mixer.forward(rt, batch, x, view))]
         return out
 
 

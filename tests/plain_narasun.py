@@ -43,13 +43,17 @@ def dense_ff(t, p, h, rd=ident):
     return swiglu(h, t[p + "gate"], t[p + "up"], t[p + "down"], rd)
 
 
-def moe_ff(t, p, h, n_experts, top, rd=ident):
-    """Sigmoid router; the `top` best experts; each gets score * h as its input; outputs added."""
+def moe_ff(t, p, h, n_experts, top, rd=ident, choice=None):
+    """Sigmoid router; the `top` best experts; each gets score * h as its input; outputs added.
+    choice ([tokens, top] expert ids) replaces the router's decision (not its scores): a comparison with an
+    engine in a format whose rounding may turn a close call the other way then rests on the arithmetic alone."""
     z = h @ t[p + "router"].T
     s = torch.sigmoid(z)
     out = torch.zeros_like(h)
     for i in range(h.shape[0]):
         order = sorted(range(n_experts), key=lambda e: (-float(s[i, e]), e))[:top]
+        if choice is not None:
+            order = [int(e) for e in choice[i]]
         for e in order:
             q = f"{p}e{e}."
             out[i] += swiglu(rd(s[i, e] * h[i]), t[q + "gate"], t[q + "up"], t[q + "down"], rd)
@@ -155,12 +159,12 @@ def mixer(t, l, h, layer, eps, rd=ident):
     raise ValueError(kind)
 
 
-def feed_forward(t, l, h, mlp, rd=ident):
+def feed_forward(t, l, h, mlp, rd=ident, choice=None):
     if mlp is None:
         return torch.zeros_like(h)
     if mlp["kind"] == "dense":
         return dense_ff(t, f"l{l}.mlp.", h, rd)
-    return moe_ff(t, f"l{l}.mlp.", h, mlp["router"]["experts"], mlp["router"]["top"], rd)
+    return moe_ff(t, f"l{l}.mlp.", h, mlp["router"]["experts"], mlp["router"]["top"], rd, choice)
 
 
 def layer_order(cfg):
@@ -176,10 +180,12 @@ def layer_order(cfg):
     return out
 
 
-def forward(cfg, t, tokens, dtype=torch.float64, streams=None, bf16=False):
+def forward(cfg, t, tokens, dtype=torch.float64, streams=None, bf16=False, choices=None):
     """Logits [T, vocab] of one sequence from its first token; `streams` (a list) receives the residual
-    stream after every layer run.  bf16: round where a bfloat16 engine stores activations."""
+    stream after every layer run.  bf16: round where a bfloat16 engine stores activations.  choices: per run
+    of a routed feed-forward, in the order of the runs, the experts to use ([tokens, top]; see moe_ff)."""
     rd = to_bf16 if bf16 else ident
+    routed = 0
     t = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in t.items()}
     eps = cfg["norm"]["eps"]
     x = t["embed"][torch.as_tensor(tokens)]
@@ -189,7 +195,10 @@ def forward(cfg, t, tokens, dtype=torch.float64, streams=None, bf16=False):
             x = rd(torch.cat([x, x0], -1)) @ t["loop.in"].T + t["loop.step"][begins]
         layer = cfg["layers"][l]
         h = rd(offset_norm(x, t[f"l{l}.norm1"], eps))
-        x = x + (mixer(t, l, h, layer, eps, rd) + feed_forward(t, l, h, layer.get("mlp"), rd))
+        choice = None
+        if choices is not None and (layer.get("mlp") or {}).get("kind") == "moe":
+            choice, routed = choices[routed], routed + 1
+        x = x + (mixer(t, l, h, layer, eps, rd) + feed_forward(t, l, h, layer.get("mlp"), rd, choice))
         if streams is not None:
             streams.append(x.clone())
     return rd(offset_norm(x, t["final.norm"], eps)) @ t["head"].T

@@ -12,11 +12,13 @@ import tiny_narasun as tiny
 pytestmark = pytest.mark.gpu
 
 TOL_F32 = 3e-5            # largest |engine - plain| relative to the largest |logit|: float32 sums against float64
-# bfloat16: a row's error relative to the row's largest logit.  The storage format alone costs about 0.01 on
-# these models (the plain implementation with roundings to bfloat16 says so), and a router whose two best
-# scores are closer than that rounding may pick the other expert for a token, in either implementation:
-# most rows must be close, and the typical row as close as the yardstick.
-BF16_TYPICAL, BF16_ROW, BF16_ROWS_OVER = 0.02, 0.06, 0.15
+# bfloat16: a row's error relative to the row's largest logit.  The yardstick is the plain implementation with
+# roundings to bfloat16 where an engine stores activations: its distance from the exact result is what the storage
+# format alone costs on this input (0.005 to 0.03 for the typical row of these models, more in a matrix memory's
+# first rows, whose normaliser is small).  A router whose two best scores are closer than that rounding may pick
+# the other expert for a token, in either implementation, so single rows may be far off in both: the engine's
+# typical row must be as close as the yardstick's (twice its median), and few rows may be far beyond its 90th percentile.
+BF16_FACTOR, BF16_SLACK, BF16_ROWS_OVER = 2.0, 0.004, 0.15
 
 
 @pytest.fixture(scope="module")
@@ -48,58 +50,102 @@ def row_errs(got, ref):
 
 
 def check(got, ref, dtype):
+    """ref: the exact logits, or (exact, the yardstick's) for bfloat16."""
+    same = None
+    if isinstance(ref, tuple):
+        ref, same = ref
     assert got.shape == ref.shape
     assert bool(torch.isfinite(got).all())
     errs = row_errs(got, ref)
     if dtype == "float32":
         assert float(errs.max()) < TOL_F32, float(errs.max())
     else:
-        assert float(errs.median()) < BF16_TYPICAL, float(errs.median())
-        assert float((errs > BF16_ROW).double().mean()) <= BF16_ROWS_OVER, errs
+        yard = row_errs(same, ref)
+        assert float(errs.median()) < BF16_FACTOR * float(yard.median()) + BF16_SLACK, (float(errs.median()), float(yard.median()))
+        far = 3.0 * float(torch.quantile(yard, 0.9)) + 4 * BF16_SLACK
+        assert float((errs > far).double().mean()) <= BF16_ROWS_OVER, (errs, far)
 
 
-def exact(plains, name, tokens):
+def exact(plains, name, tokens, dtype="float32", choices=None):
+    """The plain implementation's logits; for bfloat16 with the yardstick's beside them, both with the experts
+    that the engine chose (`choices`, from run_alone): a router's close call may fall the other way in bfloat16,
+    in either implementation, and would then hide what the comparison is about (float32 compares the choice too)."""
     cfg, tensors = plains[name]
-    return plain.forward(cfg, tensors, tokens)
+    ref = plain.forward(cfg, tensors, tokens, choices=choices)
+    if dtype == "bfloat16":
+        return ref, plain.forward(cfg, tensors, tokens, bf16=True, choices=choices)
+    return ref
 
 
-def run_alone(engine, tokens, cuts):
-    """One request through the engine in steps of the given sizes (the rest token by token); every logit."""
+def run_alone(engine, tokens, cuts, choices=None):
+    """One request through the engine in steps of the given sizes (the rest token by token); every logit.
+    choices (a list): receives, per run of a routed feed-forward, the experts chosen for every token."""
+    from catena_models_b200 import kernels
+
     (slot,) = engine.admit(1)
     out, at = [], 0
+    route, per_step = kernels.moe_route, []
+
+    def spy(ids, wts, perm, dest, work, h, w_router, tok_seq, top, *a, **k):
+        route(ids, wts, perm, dest, work, h, w_router, tok_seq, top, *a, **k)
+        if not torch.cuda.is_current_stream_capturing():
+            per_step[-1].append(ids.view(-1, top).cpu())
+
     try:
+        if choices is not None:
+            kernels.moe_route = spy
         for n in list(cuts) + [1] * len(tokens):
             if at >= len(tokens):
                 break
             part = tokens[at:at + n]
+            per_step.append([])
             out.append(engine.step([slot], [part], [list(range(len(part)))]).float().cpu())
+            per_step[-1] = [ids[:len(part)] for ids in per_step[-1]]
             at += len(part)
         engine.check_errors()
     finally:
+        kernels.moe_route = route
         engine.release([slot])
+    if choices is not None and per_step and per_step[0]:
+        choices.extend(torch.cat([step[c] for step in per_step]) for c in range(len(per_step[0])))
     return torch.cat(out)
+
+
+def engine_for(folders, name, dtype):
+    """The module's engine for a model and dtype.  bfloat16 engines of models with a router run kernel by kernel:
+    a replayed recording does not pass through the call that `run_alone` listens to (recorded steps are compared
+    in float32, and in bfloat16 on model D, which has no router)."""
+    routed = any((l.get("mlp") or {}).get("kind") == "moe" for l in tiny.ALL[name]["layers"])
+    return model_for(folders, name, dtype, **({"use_graphs": False} if dtype == "bfloat16" and routed else {})).engine
+
+
+def compare_alone(engine, plains, name, tokens, cuts, dtype):
+    """run_alone against the plain implementation (in bfloat16 with the engine's own choice of experts)."""
+    choices = [] if dtype == "bfloat16" else None
+    got = run_alone(engine, tokens, cuts, choices)
+    check(got, exact(plains, name, tokens, dtype, choices or None), dtype)
+    return got
 
 
 @pytest.mark.parametrize("name", list(tiny.ALL))
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_whole_prompts(folders, plains, name, dtype):
     """Each mechanism's own model and the mixed ones: prompts of 1, 2 and some dozens of tokens, every position."""
-    engine = model_for(folders, name, dtype).engine
+    engine = engine_for(folders, name, dtype)
     vocab = plains[name][0]["vocab"]
     for n, seed in ((1, 1), (2, 2), (37, 3), (131, 4)):
         tokens = tiny.prompt(n, vocab, seed)
-        check(run_alone(engine, tokens, [n]), exact(plains, name, tokens), dtype)
+        compare_alone(engine, plains, name, tokens, [n], dtype)
 
 
-@pytest.mark.parametrize("name", ["P", "Q", "R"])
+@pytest.mark.parametrize("name", ["P", "Q", "R", "D"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_decoding_continues_a_prompt(folders, plains, name, dtype):
     """40 tokens in one step, then 50 one by one (across the border of a cache page at 64): the state and
     the cache carry everything the later tokens need."""
-    engine = model_for(folders, name, dtype).engine
+    engine = engine_for(folders, name, dtype)
     tokens = tiny.prompt(90, plains[name][0]["vocab"], 5)
-    got = run_alone(engine, tokens, [40])
-    check(got, exact(plains, name, tokens), dtype)
+    compare_alone(engine, plains, name, tokens, [40], dtype)
 
 
 @pytest.mark.parametrize("name", ["P", "Q", "R"])
@@ -115,18 +161,18 @@ def test_token_by_token_equals_prompt(folders, name):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_portions(folders, plains, name, dtype):
     """A prompt in portions of several sizes, down to two tokens, some ending on a page border."""
-    engine = model_for(folders, name, dtype).engine
+    engine = engine_for(folders, name, dtype)
     tokens = tiny.prompt(150, plains[name][0]["vocab"], 7)
-    ref = exact(plains, name, tokens)
     for cuts in ([2, 2, 60, 3, 61, 22], [64, 64, 2, 20], [7] * 22, [1, 2, 127, 20]):
-        check(run_alone(engine, tokens, cuts), ref, dtype)
+        compare_alone(engine, plains, name, tokens, cuts, dtype)
 
 
-@pytest.mark.parametrize("name", ["P", "Q", "R"])
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,dtype", [("P", "float32"), ("Q", "float32"), ("R", "float32"), ("D", "bfloat16"),
+                                        ("attention_mix", "bfloat16"), ("memory", "bfloat16")])
 def test_unequal_batch_against_each_alone(folders, plains, name, dtype):
     """Four requests of unequal lengths start together and decode together; the short ones end early, and
-    their slots serve a second batch at once.  Every request must come out as it does alone."""
+    their slots serve a second batch at once.  Every request must come out as it does alone.  (bfloat16 on the
+    models without a router: see `exact`.)"""
     engine = model_for(folders, name, dtype).engine
     vocab = plains[name][0]["vocab"]
     for round_ in range(2):
@@ -152,7 +198,7 @@ def test_unequal_batch_against_each_alone(folders, plains, name, dtype):
         engine.check_errors()
         for i, r in enumerate(reqs):
             mine = torch.cat(got[i])
-            check(mine, exact(plains, name, r), dtype)
+            check(mine, exact(plains, name, r, dtype), dtype)
             if dtype == "float32":
                 assert float(row_errs(mine, run_alone(engine, r, [lens[i]])).max()) < TOL_F32
 
@@ -176,9 +222,9 @@ def test_long_decoding(folders, plains, dtype):
     """Decoding from 200 to 330 tokens: past the 256 entries of one decode-attention chunk and across three page
     borders, with the query temperature changing every few tokens."""
     name = "Q"
-    engine = model_for(folders, name, dtype).engine
+    engine = engine_for(folders, name, dtype)
     tokens = tiny.prompt(330, plains[name][0]["vocab"], 40)
-    check(run_alone(engine, tokens, [200]), exact(plains, name, tokens), dtype)
+    compare_alone(engine, plains, name, tokens, [200], dtype)
 
 
 def test_a_far_key_and_a_sink_show(folders, plains):
@@ -222,8 +268,9 @@ def test_long_prompts_on_the_tensor_core_attention(tmp_path, head):
     engine.check_errors()
     engine.release(slots)
     ra, rb = plain.forward(pc, pt, a + [5]), plain.forward(pc, pt, b + [6])
-    check(got, torch.cat([ra[want[0]], rb[want[1]]]), "bfloat16")
-    check(nxt, torch.stack([ra[-1], rb[-1]]), "bfloat16")
+    ya, yb = plain.forward(pc, pt, a + [5], bf16=True), plain.forward(pc, pt, b + [6], bf16=True)
+    check(got, (torch.cat([ra[want[0]], rb[want[1]]]), torch.cat([ya[want[0]], yb[want[1]]])), "bfloat16")
+    check(nxt, (torch.stack([ra[-1], rb[-1]]), torch.stack([ya[-1], yb[-1]])), "bfloat16")
 
 
 @pytest.mark.parametrize("name", ["P", "R"])

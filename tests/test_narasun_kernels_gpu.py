@@ -80,7 +80,10 @@ def test_residual_sum_and_norm(dtype):
     bias, w = rnd(H, seed=6), rnd(H, seed=7)
     ref = h.double() + (0.7 * a.double() + 1.3 * b.double().view(rows, 3, H).sum(1)) + bias.double()
     n = torch.empty((rows, H), dtype=dtype, device=DEV)
-    kernels.residual_add_norm(h, kernels.Terms([(a, 0.7, 1), (b, 1.3, 3)]), n, w, 1e-5, bias)
+    order = torch.randperm(rows * 3, device=DEV).to(torch.int32)
+    shuffled = torch.empty_like(b)
+    shuffled[order.long()] = b
+    kernels.residual_add_norm(h, kernels.Terms([(a, 0.7, 1), (shuffled, 1.3, 3, order)]), n, w, 1e-5, bias)
     close(h, ref, 1e-6)
     close(n, plain.rms_unit(ref, 1e-5) * w.double(), 1e-6 if dtype == torch.float32 else 1e-2)
     y = torch.empty((rows, H), dtype=dtype, device=DEV)
@@ -214,14 +217,37 @@ def test_routed_feed_forward(dtype, tol, T, E, top):
     tok_seq[T - 1] = -1                                                     # a row of padding
     P = T * top
     tiles = kernels.moe_max_tiles(P, E)
+    rows = tiles * kernels.MOE_TILE_SIMT
     ids, wts = torch.empty(P, dtype=torch.int32, device=DEV), torch.empty(P, device=DEV)
-    perm, work = torch.empty(P, dtype=torch.int32, device=DEV), torch.empty(2 * E + 1 + 3 * tiles, dtype=torch.int32, device=DEV)
-    kernels.moe_route(ids, wts, perm, work, h, wr, tok_seq, top)
-    a = torch.empty((P, F), dtype=dtype, device=DEV)
+    perm, dest = torch.empty(rows, dtype=torch.int32, device=DEV), torch.empty(P, dtype=torch.int32, device=DEV)
+    work = torch.empty(kernels.moe_work_size(P, E), dtype=torch.int32, device=DEV)
+    kernels.moe_route(ids, wts, perm, dest, work, h, wr, tok_seq, top)
+    a = torch.empty((rows, F), dtype=dtype, device=DEV)
     kernels.moe_grouped(a, h, w_up, work, perm, wts, top, tiles, up=True, apply_weight=True)
-    y = torch.zeros((P, W), device=DEV)
+    y = torch.zeros((rows, W), device=DEV)
     kernels.moe_grouped(y, a, w_down, work, perm, wts, top, tiles, up=False, apply_weight=False)
-    got = y.view(T, top, W).sum(1)[:T - 1]
+    where = dest.view(T, top)[:T - 1].long()
+    got = y[where].sum(1)
+    if dtype == torch.bfloat16:
+        # the same rows through the grouped tcgen05 product (row tiles of 128)
+        big = kernels.MOE_TILE_TC
+        tiles2 = kernels.moe_max_tiles(P, E, big)
+        rows2 = tiles2 * big
+        perm2, dest2 = torch.empty(rows2, dtype=torch.int32, device=DEV), torch.empty(P, dtype=torch.int32, device=DEV)
+        work2 = torch.empty(kernels.moe_work_size(P, E, big), dtype=torch.int32, device=DEV)
+        ids2, wts2 = torch.empty_like(ids), torch.empty_like(wts)
+        kernels.moe_route(ids2, wts2, perm2, dest2, work2, h, wr, tok_seq, top, tile_rows=big)
+        assert torch.equal(ids2, ids)
+        groups = kernels.moe_tile_group(work2, P, E, big)
+        xs = torch.empty((rows2, W), dtype=dtype, device=DEV)
+        kernels.moe_gather(xs, h, dest2, wts2, top, True)
+        a2 = torch.empty((rows2, F), dtype=dtype, device=DEV)
+        kernels.gemm_tc_grouped(a2, xs, w_up, groups, swiglu=True, block_n=128)
+        y2 = torch.empty((rows2, W), device=DEV)
+        kernels.gemm_tc_grouped(y2, a2, w_down, groups, block_n=128)
+        got2 = y2[dest2.view(T, top)[:T - 1].long()].sum(1)
+        assert float((got2 - got).abs().max() / got.abs().max()) < 2e-2
+        got = got2
     hd = h.double().cpu()
     s = torch.sigmoid(hd @ wr.double().cpu().T)
     rdt = (lambda x: x.to(dtype).double())
@@ -236,4 +262,4 @@ def test_routed_feed_forward(dtype, tol, T, E, top):
             g, u = w_up[e, :F].double().cpu() @ x, w_up[e, F:].double().cpu() @ x
             ref[t] += w_down[e].double().cpu() @ rdt(plain.silu(g) * u)
     close(got, ref, tol)
-    assert bool((ids.view(T, top)[T - 1] == -1).all())
+    assert bool((ids.view(T, top)[T - 1] == -1).all()) and bool((dest.view(T, top)[T - 1] == -1).all())

@@ -54,6 +54,9 @@ TINY_R = dict(architecture="Narasun", vocab=96, width=32, norm=dict(eps=1e-6), l
     parallel(attention(2, 2, 16, 8, 0.25, 0.5, 64), 2, 8, 4, 0.8, 0.9, moe(16, 4, 3)),
     mlstm(2, 8, 16, 12.0, dense(48), "_2")])
 
+# D: P with dense feed-forwards in place of the routed ones (nothing in it decides between alternatives)
+TINY_D = dict(TINY_P, layers=[mlstm(2, 16, 24, 10.0, dense(40)), TINY_P["layers"][1], TINY_P["layers"][2]])
+
 # one mechanism at a time
 ONLY_ATTENTION_MIX = dict(architecture="Narasun", vocab=64, width=32, norm=dict(eps=1e-6), loop=None, layers=[
     parallel(attention(2, 1, 16, 16, 0.25, 0.7, 4), 2, 16, 4, 1.0, 1.0, None)])
@@ -64,7 +67,7 @@ ONLY_MEMORY_MOE = dict(architecture="Narasun", vocab=64, width=40, norm=dict(eps
 ONLY_LOOP = dict(architecture="Narasun", vocab=64, width=24, norm=dict(eps=1e-6), loop=dict(start=0, stop=1, times=2), layers=[
     mlstm(1, 8, 8, 6.0, dense(32))])
 
-ALL = {"P": TINY_P, "Q": TINY_Q, "R": TINY_R, "attention_mix": ONLY_ATTENTION_MIX, "memory": ONLY_MEMORY,
+ALL = {"P": TINY_P, "Q": TINY_Q, "R": TINY_R, "D": TINY_D, "attention_mix": ONLY_ATTENTION_MIX, "memory": ONLY_MEMORY,
        "memory_moe": ONLY_MEMORY_MOE, "loop": ONLY_LOOP}
 
 
