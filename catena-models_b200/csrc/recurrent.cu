@@ -141,6 +141,43 @@ extern "C" int cm_lowrank_decay(int dt, float* out, const void* x, const void* w
     return CM_OK;
 }
 
+// The decay network through the runtime's products (ranks that fill a tensor-core tile): tanh in place on the
+// first product's result, and w = exp(-exp(z + w0)) from the second product's float result.
+template <typename T>
+__global__ void tanh_inplace_kernel(T* __restrict__ x, long long n) {
+    pdl_trigger();
+    pdl_wait();
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        x[i] = from_f32<T>(tanhf(to_f32(x[i])));
+}
+
+__global__ void decay_from_logits_kernel(float* __restrict__ out, const float* __restrict__ z, const float* __restrict__ w0,
+                                         long long n, int C) {
+    pdl_trigger();
+    pdl_wait();
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        out[i] = expf(-expf(z[i] + w0[i % C]));
+}
+
+extern "C" int cm_tanh_inplace(int dt, void* x, long long n, cudaStream_t st) {
+    if (n <= 0) return CM_OK;
+    const unsigned grid = (unsigned)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+    if (dt == DT_F32) cm_launch(tanh_inplace_kernel<float>, grid, 256, 0, st, (float*)x, n);
+    else if (dt == DT_BF16) cm_launch(tanh_inplace_kernel<bf16>, grid, 256, 0, st, (bf16*)x, n);
+    else return CM_ERR_DTYPE;
+    CM_CHECK_LAUNCH();
+    return CM_OK;
+}
+
+extern "C" int cm_decay_from_logits(float* out, const float* z, const float* w0, long long rows, int C, cudaStream_t st) {
+    const long long n = rows * C;
+    if (n <= 0) return CM_OK;
+    const unsigned grid = (unsigned)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+    cm_launch(decay_from_logits_kernel, grid, 256, 0, st, out, z, w0, n, C);
+    CM_CHECK_LAUNCH();
+    return CM_OK;
+}
+
 __device__ __forceinline__ float log_sigmoid_f32(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
 // Capped gate pre-activations of the matrix memory: z = W h + b for 2 * H rows of W (input gates, then
@@ -442,15 +479,17 @@ extern "C" int cm_matrix_scan(int dt, int mode, const ScanArgs* args, int B, cud
     if (B <= 0 || a.rows <= 0) return CM_OK;
     if (a.D <= 0 || a.DV <= 0 || a.D > 1024) CM_REFUSE("matrix_scan: head sizes %d x %d (keys up to 1024)", a.D, a.DV);
     if (!a.raw) CM_REFUSE("matrix_scan: the float buffer for the heads' raw outputs is missing");
-    // Channels per thread (a power of two from 2 to 32) and parts per column (a power of two up to 32: the parts of
-    // a column share a warp): as many channels as leave the grid with about two blocks per SM.
+    // Channels per thread (a power of two from 2 to 32) and parts per column (a power of two up to 32): as many
+    // channels as leave the grid with a block per SM.  The walk is bound by its latency per row, not by arithmetic,
+    // so what counts is how many SMs walk at once (measured on B200, 2,048 rows, one sequence, 8 heads of 64 x 128 /
+    // 16 heads of 64 x 64, us at 2 / 4 / 8 / 16 / 32 channels: 541 / 407 / 619 / 959 / 1255 and 293 / 331 / 509 / 769 / 1229).
     auto parts_for = [&](int r) { int k = 1; while (k * r < a.D) k *= 2; return k; };
     auto blocks = [&](int k) {
         const int real = SCAN_THREADS / k - (mode == 1 ? 1 : 0);
         return real < 1 ? 0LL : (long long)a.H * ((a.DV + real - 1) / real) * B;
     };
     int rpt = 32;
-    while (rpt > 2 && parts_for(rpt / 2) <= 32 && blocks(parts_for(rpt)) < 2 * 148) rpt /= 2;
+    while (rpt > 2 && parts_for(rpt / 2) <= 32 && blocks(parts_for(rpt)) < 148) rpt /= 2;
     const int ks = parts_for(rpt);
     if (ks > 32) CM_REFUSE("matrix_scan: heads of %d key channels (up to 1024)", a.D);
     a.KS = ks;

@@ -59,6 +59,8 @@ _SIGNATURES = {
     "cm_shift_mix": [_i, _vp, _vp, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _i, _ll, _i, _vp],
     "cm_lowrank_decay": [_i, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _vp],
     "cm_capped_gates": [_i, _vp, _vp, _vp, _vp, _f, _ll, _i, _i, _vp],
+    "cm_tanh_inplace": [_i, _vp, _ll, _vp],
+    "cm_decay_from_logits": [_vp, _vp, _vp, _ll, _i, _vp],
     "cm_matrix_scan": [_i, _i, _vp, _i, _vp],
     "cm_moe_route": [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _i, _vp],
     "cm_moe_gather": [_i, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _vp],
@@ -791,6 +793,19 @@ def lowrank_decay(out, x, w1, w2, w0):
     _check(lib().cm_lowrank_decay(dtype_code(x.dtype), _ptr(out), _ptr(x), _ptr(w1), _ptr(w2), _ptr(w0), rows, W, R, C,
                                   _stream()), "lowrank_decay",
            cost=lambda: (f"{rows}x{W} rank {R} -> {C}", _nbytes(x, out, w1, w2), 2 * rows * R * (W + C)))
+
+
+def tanh_inplace(x):
+    """x <- tanh(x), in x's dtype (contiguous)."""
+    _check(lib().cm_tanh_inplace(dtype_code(x.dtype), _ptr(x), x.numel(), _stream()), "tanh_inplace",
+           cost=lambda: (f"{tuple(x.shape)}", 2 * _nbytes(x), 0))
+
+
+def decay_from_logits(out, z, w0):
+    """out = exp(-exp(z + w0)): z, out float32 [rows, C] contiguous, w0 float32 [C]."""
+    rows, C = z.shape
+    _check(lib().cm_decay_from_logits(_ptr(out), _ptr(z), _ptr(w0), rows, C, _stream()), "decay_from_logits",
+           cost=lambda: (f"{rows}x{C}", _nbytes(z, out), 0))
 
 
 def capped_gates(out, x, w, bias, cap):

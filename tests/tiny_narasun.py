@@ -36,10 +36,11 @@ def moe(ff, experts, top):
     return dict(kind="moe", expert=dict(ff=ff), router=dict(experts=experts, top=top))
 
 
-# P: a loop inside the stack whose first layer is a matrix memory; two experts per token; a layer without feed-forward
+# P: a loop inside the stack whose first layer is a matrix memory; two experts per token; a layer without feed-forward;
+# a decay network wide enough (rank 32) to run as two products
 TINY_P = dict(architecture="Narasun", vocab=200, width=64, norm=dict(eps=1e-5), loop=dict(start=0, stop=2, times=2), layers=[
     mlstm(2, 16, 24, 10.0, moe(40, 5, 2)),
-    parallel(attention(4, 2, 16, 16, 0.3, 0.4, 8), 2, 16, 8, 0.7, 1.1, dense(96)),
+    parallel(attention(4, 2, 16, 16, 0.3, 0.4, 8), 2, 16, 32, 0.7, 1.1, dense(96)),
     mlstm(4, 8, 8, 8.0, None, "_3")])
 
 # Q: no loop; value heads larger than query heads (and no multiple of 16); one key/value head per query head, and one
