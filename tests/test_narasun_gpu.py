@@ -138,7 +138,7 @@ def test_whole_prompts(folders, plains, name, dtype):
         compare_alone(engine, plains, name, tokens, [n], dtype)
 
 
-@pytest.mark.parametrize("name", ["P", "Q", "R", "D"])
+@pytest.mark.parametrize("name", ["P", "Q", "R", "D", "O"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_decoding_continues_a_prompt(folders, plains, name, dtype):
     """40 tokens in one step, then 50 one by one (across the border of a cache page at 64): the state and

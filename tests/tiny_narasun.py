@@ -58,6 +58,11 @@ TINY_R = dict(architecture="Narasun", vocab=96, width=32, norm=dict(eps=1e-6), l
 # D: P with dense feed-forwards in place of the routed ones (nothing in it decides between alternatives)
 TINY_D = dict(TINY_P, layers=[mlstm(2, 16, 24, 10.0, dense(40)), TINY_P["layers"][1], TINY_P["layers"][2]])
 
+# O: sizes that are multiples of nothing convenient (width 36, heads of 12 and 20, 77 tokens, rank 5, an inner width of 28)
+TINY_O = dict(architecture="Narasun", vocab=77, width=36, norm=dict(eps=1e-5), loop=dict(start=1, stop=2, times=2), layers=[
+    parallel(attention(2, 1, 12, 20, 0.3, 0.2, 7), 1, 12, 5, 1.0, 1.0, moe(20, 3, 2)),
+    mlstm(3, 12, 20, 9.0, dense(28))])
+
 # one mechanism at a time
 ONLY_ATTENTION_MIX = dict(architecture="Narasun", vocab=64, width=32, norm=dict(eps=1e-6), loop=None, layers=[
     parallel(attention(2, 1, 16, 16, 0.25, 0.7, 4), 2, 16, 4, 1.0, 1.0, None)])
@@ -68,7 +73,7 @@ ONLY_MEMORY_MOE = dict(architecture="Narasun", vocab=64, width=40, norm=dict(eps
 ONLY_LOOP = dict(architecture="Narasun", vocab=64, width=24, norm=dict(eps=1e-6), loop=dict(start=0, stop=1, times=2), layers=[
     mlstm(1, 8, 8, 6.0, dense(32))])
 
-ALL = {"P": TINY_P, "Q": TINY_Q, "R": TINY_R, "D": TINY_D, "attention_mix": ONLY_ATTENTION_MIX, "memory": ONLY_MEMORY,
+ALL = {"P": TINY_P, "Q": TINY_Q, "R": TINY_R, "D": TINY_D, "O": TINY_O, "attention_mix": ONLY_ATTENTION_MIX, "memory": ONLY_MEMORY,
        "memory_moe": ONLY_MEMORY_MOE, "loop": ONLY_LOOP}
 
 
