@@ -145,6 +145,107 @@ extern "C" int cm_moe_gather(int dt, void* xs, const void* h, const int* dest, c
     return CM_OK;
 }
 
+// Everything above in one block, for the few rows of a decode step: scores, the best `top`, counts, the list of
+// row tiles, the order of the pairs, and (with xs) the experts' inputs in that order.  One launch instead of five.
+#define MOE_SMALL_ROWS 64
+#define MOE_SMALL_SCORES 8192
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_route_small_kernel(int* __restrict__ ids, float* __restrict__ wts, int* __restrict__ perm, int* __restrict__ dest,
+                       int* __restrict__ counts_out, int* __restrict__ plan, int* __restrict__ tile_group,
+                       const T* __restrict__ h, const T* __restrict__ wr, const int* __restrict__ tok_seq, int rows, int W,
+                       int E, int top, int softmax_gate, int renormalize, int tile_rows, int max_tiles,
+                       T* __restrict__ xs, int apply_weight) {
+    extern __shared__ float score[];              // [rows][E], then E counts and E cursors
+    int* counts = reinterpret_cast<int*>(score + rows * E);
+    int* cursor = counts + E;
+    pdl_trigger();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
+    for (int pe = warp; pe < rows * E; pe += 8) {
+        const int t = pe / E, e = pe - t * E;
+        const T* w = wr + (long long)e * W;
+        const T* hr = h + (long long)t * W;
+        float acc = 0.f;
+        for (int c = lane; c < W; c += 32) acc = fmaf(to_f32(w[c]), to_f32(hr[c]), acc);
+        acc = warp_sum(acc);
+        if (lane == 0) score[pe] = acc;
+    }
+    __syncthreads();
+    for (int t = threadIdx.x; t < rows; t += blockDim.x) {
+        if (tok_seq && tok_seq[t] < 0) {
+            for (int j = 0; j < top; ++j) ids[t * top + j] = -1;
+            continue;
+        }
+        float* sc = score + t * E;
+        if (softmax_gate) {
+            float mx = -INFINITY, den = 0.f;
+            for (int e = 0; e < E; ++e) mx = fmaxf(mx, sc[e]);
+            for (int e = 0; e < E; ++e) den += expf(sc[e] - mx);
+            for (int e = 0; e < E; ++e) sc[e] = expf(sc[e] - mx) / den;
+        } else {
+            for (int e = 0; e < E; ++e) sc[e] = sigmoid_f32(sc[e]);
+        }
+        float total = 0.f;
+        for (int j = 0; j < top; ++j) {
+            int best = 0;
+            float bv = -INFINITY;
+            for (int e = 0; e < E; ++e)
+                if (sc[e] > bv) {
+                    bv = sc[e];
+                    best = e;
+                }
+            ids[t * top + j] = best;
+            wts[t * top + j] = bv;
+            total += bv;
+            sc[best] = -INFINITY;
+            atomicAdd(counts + best, 1);
+        }
+        if (renormalize)
+            for (int j = 0; j < top; ++j) wts[t * top + j] /= total;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int n = 0;
+        for (int e = 0; e < E; ++e) {
+            const int c = counts[e];
+            counts_out[e] = c;
+            cursor[e] = n * tile_rows;
+            for (int r = 0; r < c; r += tile_rows) {
+                plan[1 + 3 * n] = e;
+                plan[2 + 3 * n] = n * tile_rows;
+                plan[3 + 3 * n] = min(tile_rows, c - r);
+                tile_group[n] = e;
+                ++n;
+            }
+        }
+        plan[0] = n;
+        for (; n < max_tiles; ++n) tile_group[n] = 0;
+    }
+    __syncthreads();
+    const int P = rows * top;
+    for (int p = threadIdx.x; p < P; p += blockDim.x) {
+        const int e = ids[p];
+        int pos = -1;
+        if (e >= 0) {
+            pos = atomicAdd(cursor + e, 1);
+            perm[pos] = p;
+        }
+        dest[p] = pos;
+    }
+    if (!xs) return;
+    __syncthreads();                              // dest and wts of this block's own writes
+    for (int p = warp; p < P; p += 8) {
+        const int d = dest[p];
+        if (d < 0) continue;
+        const float w = apply_weight ? wts[p] : 1.f;
+        const T* src = h + (long long)(p / top) * W;
+        T* dst = xs + (long long)d * W;
+        for (int c = lane; c < W; c += 32) dst[c] = from_f32<T>(to_f32(src[c]) * w);
+    }
+}
+
 // Row tiles that `pairs` rows of `E` experts can need at most, each expert's rows starting a tile of its own.
 static int max_tiles_for(long long pairs, int E, int tile_rows) {
     const long long full = (pairs + tile_rows - 1) / tile_rows;
@@ -154,15 +255,30 @@ static int max_tiles_for(long long pairs, int E, int tile_rows) {
 // work: int32 scratch of E (counts) + E (cursor) + 1 + 3 * max_tiles (plan) + max_tiles (tile_group) entries;
 // perm: max_tiles * tile_rows entries (sorted rows), dest: P entries.  tile_rows: 32 for the CUDA-core grouped
 // products of this file, 128 for the tensor-core grouped product.
+// xs (or null): the experts' inputs [max_tiles * tile_rows][W] in the order of the experts, h times the pair's weight
+// when apply_weight (cm_moe_gather as part of this call).
 extern "C" int cm_moe_route(int dt, int* ids, float* wts, int* perm, int* dest, int* work, const void* h, const void* wr,
                             const int* tok_seq, long long rows, int W, int E, int top, int softmax_gate,
-                            int renormalize, int tile_rows, cudaStream_t st) {
+                            int renormalize, int tile_rows, void* xs, int apply_weight, cudaStream_t st) {
     if (rows <= 0) return CM_OK;
     if (top < 1 || top > E) CM_REFUSE("moe_route: %d of %d experts", top, E);
     if ((size_t)E * sizeof(float) > 48 * 1024) CM_REFUSE("moe_route: %d experts", E);
     if (tile_rows != MOE_TM && tile_rows != 128) CM_REFUSE("moe_route: row tiles of %d (32 or 128)", tile_rows);
     const int max_tiles = max_tiles_for(rows * top, E, tile_rows);
     int *counts = work, *cursor = work + E, *plan = work + 2 * E, *tile_group = plan + 1 + 3 * max_tiles;
+    if (rows <= MOE_SMALL_ROWS && rows * E <= MOE_SMALL_SCORES && (dt == DT_F32 || dt == DT_BF16)) {
+        const size_t small = ((size_t)rows * E) * sizeof(float) + 2 * (size_t)E * sizeof(int);
+        if (dt == DT_F32)
+            cm_launch(moe_route_small_kernel<float>, 1, 256, small, st, ids, wts, perm, dest, counts, plan, tile_group,
+                      (const float*)h, (const float*)wr, tok_seq, (int)rows, W, E, top, softmax_gate, renormalize, tile_rows,
+                      max_tiles, (float*)xs, apply_weight);
+        else
+            cm_launch(moe_route_small_kernel<bf16>, 1, 256, small, st, ids, wts, perm, dest, counts, plan, tile_group,
+                      (const bf16*)h, (const bf16*)wr, tok_seq, (int)rows, W, E, top, softmax_gate, renormalize, tile_rows,
+                      max_tiles, (bf16*)xs, apply_weight);
+        CM_CHECK_LAUNCH();
+        return CM_OK;
+    }
     if (cudaMemsetAsync(counts, 0, (size_t)E * sizeof(int), st) != cudaSuccess) {
         cm_set_error("moe_route: memset failed");
         return CM_ERR_LAUNCH;
@@ -182,6 +298,7 @@ extern "C" int cm_moe_route(int dt, int* ids, float* wts, int* perm, int* dest, 
     const long long P = rows * top;
     cm_launch(moe_scatter_kernel, (unsigned)((P + 255) / 256), 256, 0, st, perm, dest, cursor, ids, P);
     CM_CHECK_LAUNCH();
+    if (xs) return cm_moe_gather(dt, xs, h, dest, wts, P, top, W, apply_weight, st);
     return CM_OK;
 }
 

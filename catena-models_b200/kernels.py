@@ -62,7 +62,7 @@ _SIGNATURES = {
     "cm_tanh_inplace": [_i, _vp, _ll, _vp],
     "cm_decay_from_logits": [_vp, _vp, _vp, _ll, _i, _vp],
     "cm_matrix_scan": [_i, _i, _vp, _i, _vp],
-    "cm_moe_route": [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _i, _vp],
+    "cm_moe_route": [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _i, _vp, _i, _vp],
     "cm_moe_gather": [_i, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _vp],
     "cm_gemm_tc_grouped": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _vp, _i, _vp, _vp],
     "cm_moe_grouped": [_i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
@@ -876,18 +876,20 @@ def moe_tile_group(work, pairs, experts, tile_rows):
 
 
 def moe_route(ids, wts, perm, dest, work, h, w_router, tok_seq, top, softmax_gate=False, renormalize=False,
-              tile_rows=MOE_TILE_SIMT):
+              tile_rows=MOE_TILE_SIMT, xs=None, apply_weight=False):
     """Scores of every token's experts in float32 (sigmoid, or softmax over the experts), the `top` best
     (ids, wts: [rows * top]; -1 for rows of padding), and the pairs in the order of their experts, every expert's
     rows beginning a row tile of `tile_rows` rows: perm[sorted row] = pair (moe_max_tiles * tile_rows entries),
-    dest[pair] = sorted row (-1: none), the list of row tiles in `work` (int32, moe_work_size entries)."""
+    dest[pair] = sorted row (-1: none), the list of row tiles in `work` (int32, moe_work_size entries).  With `xs`
+    ([moe_max_tiles * tile_rows, W]) the experts' inputs are gathered into it in the same call (`moe_gather`).  A step of
+    up to 64 rows runs all of this in one launch of one block."""
     rows, W = h.shape
     E = w_router.shape[0]
     if w_router.dtype != h.dtype or not (h.is_contiguous() and w_router.is_contiguous()):
         raise KernelError("moe_route: contiguous operands of one dtype")
     _check(lib().cm_moe_route(dtype_code(h.dtype), _ptr(ids), _ptr(wts), _ptr(perm), _ptr(dest), _ptr(work), _ptr(h),
                               _ptr(w_router), _ptr(tok_seq), rows, W, E, top, int(softmax_gate), int(renormalize), tile_rows,
-                              _stream()), "moe_route", 3,
+                              _ptr(xs), int(apply_weight), _stream()), "moe_route", 1 if rows <= 64 and rows * E <= 8192 else (4 if xs is not None else 3),
            cost=lambda: (f"{rows}x{W} over {E}, top {top}", _nbytes(h, w_router), 2 * rows * E * W))
 
 

@@ -81,13 +81,13 @@ class RoutedSwiGLU(FeedForward):
         perm = torch.empty(rows, dtype=torch.int32, device=dev)
         dest = torch.empty(P, dtype=torch.int32, device=dev)
         work = torch.empty(kernels.moe_work_size(P, E, tile), dtype=torch.int32, device=dev)
-        kernels.moe_route(ids, wts, perm, dest, work, x, self.router, batch.tok_seq, top, self.softmax_gate, self.renormalize, tile)
+        xs = torch.empty((rows, self.hidden), dtype=x.dtype, device=dev) if tensor_cores else None
+        kernels.moe_route(ids, wts, perm, dest, work, x, self.router, batch.tok_seq, top, self.softmax_gate, self.renormalize, tile,
+                          xs=xs, apply_weight=self.weight_on_input)
         a = torch.empty((rows, self.intermediate), dtype=x.dtype, device=dev)
         y = torch.empty((rows, self.hidden), dtype=torch.float32, device=dev)
         if tensor_cores:
             groups = kernels.moe_tile_group(work, P, E, tile)
-            xs = torch.empty((rows, self.hidden), dtype=x.dtype, device=dev)
-            kernels.moe_gather(xs, x, dest, wts, top, self.weight_on_input)
             kernels.gemm_tc_grouped(a, xs, self.w_up, groups, swiglu=True, err=rt.error_flag,
                                     block_n=rt._tile_width(rows, 2 * self.intermediate, widths=(256, 128)))
             kernels.gemm_tc_grouped(y, a, self.w_down, groups, err=rt.error_flag, block_n=128)
