@@ -391,7 +391,7 @@ matrix_scan_kernel(const ScanArgs a, int TB) {
         }
         __syncthreads();
         // the state's walk over the group: no barrier, no exchange; a thread leaves its part of every row's output
-#pragma unroll 2
+#pragma unroll 4
         for (int tt = 0; tt < nt; ++tt) {
             float q[RPT], k[RPT], w[RPT];
             load_run<RPT>(sq + (size_t)tt * Dp + i0, q);
@@ -490,6 +490,9 @@ extern "C" int cm_matrix_scan(int dt, int mode, const ScanArgs* args, int B, cud
     };
     int rpt = 32;
     while (rpt > 2 && parts_for(rpt / 2) <= 32 && blocks(parts_for(rpt)) < 148) rpt /= 2;
+    // ... and, while a thread still has more than four channels, with nearly two: several sequences in a step give the
+    // schedulers warps to choose from (2,048 rows as 4 / 8 sequences, matrix memory: 288 -> 197 and 203 -> 187 us)
+    while (rpt > 4 && parts_for(rpt / 2) <= 32 && blocks(parts_for(rpt)) < 256) rpt /= 2;
     const int ks = parts_for(rpt);
     if (ks > 32) CM_REFUSE("matrix_scan: heads of %d key channels (up to 1024)", a.D);
     a.KS = ks;
