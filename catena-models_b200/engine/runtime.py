@@ -30,6 +30,9 @@ class Runtime:
         # False: prompt steps (more than one row a sequence) run their products and attention on the CUDA
         # cores, whatever the dtype: the reference's --no-wmma-prefill (src/main.rs:34-40)
         self.tensor_core_prompts = True
+        # False: a routed feed-forward runs its experts' products on the CUDA cores also in bfloat16 (row tiles of 32
+        # instead of the grouped tcgen05 product over row tiles of 128); tests compare the two
+        self.grouped_tensor_cores = True
         self._in_prompt = False
         self._scratch = {}
         self._choices = {}                  # kernel choices by shape, so that a step from Python does not redo them

@@ -72,7 +72,7 @@ class RoutedSwiGLU(FeedForward):
         # bfloat16 with rows that TMA can fetch: the grouped tcgen05 product over row tiles of 128; else the CUDA cores
         tensor_cores = (x.dtype == torch.bfloat16 and not self.gelu and self.hidden % 8 == 0 and self.intermediate % 8 == 0
                         and self.weight_on_input and (rt.tensor_core_prompts or batch.kind == "decode")
-                        and getattr(rt, "grouped_tensor_cores", True))
+                        and rt.grouped_tensor_cores)
         tile = kernels.MOE_TILE_TC if tensor_cores else kernels.MOE_TILE_SIMT
         max_tiles = kernels.moe_max_tiles(P, E, tile)
         rows = max_tiles * tile

@@ -263,3 +263,24 @@ def test_routed_feed_forward(dtype, tol, T, E, top):
             ref[t] += w_down[e].double().cpu() @ rdt(plain.silu(g) * u)
     close(got, ref, tol)
     assert bool((ids.view(T, top)[T - 1] == -1).all()) and bool((dest.view(T, top)[T - 1] == -1).all())
+
+
+def test_routed_feed_forward_paths_agree_in_a_model(tmp_path):
+    """The grouped tcgen05 product and the CUDA-core grouped products give a bfloat16 model the same logits up to
+    rounding (a model whose two experts are both chosen for every token, so that no choice can fall differently)."""
+    import tiny_narasun as tiny
+    from catena_models_b200.api import Model
+
+    cfg = dict(architecture="Narasun", vocab=64, width=64, norm=dict(eps=1e-6), loop=None, layers=[
+        tiny.mlstm(2, 16, 16, 8.0, tiny.moe(40, 2, 2))])
+    folder = tiny.make_folder(tmp_path, "both", seed=5, config=cfg)
+    tokens = tiny.prompt(150, 64, 9)
+    out = []
+    for tensor_cores in (True, False):
+        model = Model.load(folder, dtype="bfloat16", max_tokens=512)
+        model.decoder.rt.grouped_tensor_cores = tensor_cores
+        (slot,) = model.engine.admit(1)
+        out.append(model.engine.step([slot], [tokens], [list(range(150))]).float().cpu())
+        model.engine.check_errors()
+    err = (out[0] - out[1]).abs().amax(-1) / out[1].abs().amax(-1)
+    assert float(err.median()) < 0.01 and float(err.max()) < 0.06
