@@ -114,6 +114,7 @@ class KVView:
     group: int
     owned: bool = True          # False: this layer reads a state that another layer writes
     unit: int = -1              # the state unit of the plan this view belongs to
+    borrowed: tuple = ()        # views of further units that the plan lets this layer read (PlanEntry.reads)
 
     @property
     def ring(self):
@@ -127,6 +128,7 @@ class FixedView:
     tensor: torch.Tensor        # [slots, *shape]
     owned: bool = True
     unit: int = -1
+    borrowed: tuple = ()
 
 
 @dataclasses.dataclass
@@ -136,6 +138,7 @@ class CompositeView:
     views: list
     owned: bool = True
     unit: int = -1
+    borrowed: tuple = ()
 
 
 class Cache:

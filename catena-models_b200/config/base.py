@@ -110,6 +110,35 @@ class Reader:
             raise ConfigError(f"{self.where}: " + "; ".join(self.problems))
 
 
+class _Prefixed:
+    """A sub-section's problems land in its parent's list, with the section's path in front."""
+
+    def __init__(self, target, prefix):
+        self.target, self.prefix = target, prefix
+
+    def append(self, text):
+        self.target.append(self.prefix + text)
+
+    def __bool__(self):
+        return False
+
+
+def section(r, data, key, where, required=True):
+    """A `Reader` over the object `data[key]` of a nested config.json whose problems are collected by the
+    reader `r` with the section's path (`where` + key) in front; None if the section is absent."""
+    v = data.get(key) if isinstance(data, dict) else None
+    if v is None:
+        if required:
+            r.problem(f"missing section '{where}{key}'")
+        return None
+    if not isinstance(v, dict):
+        r.problem(f"'{where}{key}' must be an object")
+        return None
+    sub = Reader(v, f"{where}{key}")
+    sub.problems = _Prefixed(r.problems, f"{where}{key}: ")
+    return sub
+
+
 def read_config_json(folder):
     path = os.path.join(folder, "config.json")
     try:

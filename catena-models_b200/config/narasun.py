@@ -16,7 +16,7 @@ from __future__ import annotations
 import dataclasses
 
 from ..csrc import limits
-from .base import ConfigError, Reader
+from .base import ConfigError, Reader, section as _section
 
 MIXER_TYPES = ("parallel", "mlstm")
 MLP_KINDS = ("dense", "moe")
@@ -83,33 +83,6 @@ class LoopConfig:
     start: int
     stop: int
     times: int
-
-
-def _section(r, data, key, where, required=True):
-    v = data.get(key) if isinstance(data, dict) else None
-    if v is None:
-        if required:
-            r.problem(f"missing section '{where}{key}'")
-        return None
-    if not isinstance(v, dict):
-        r.problem(f"'{where}{key}' must be an object")
-        return None
-    sub = Reader(v, f"{where}{key}")
-    sub.problems = _Prefixed(r.problems, f"{where}{key}: ")
-    return sub
-
-
-class _Prefixed:
-    """A sub-section's problems land in its parent's list, with the section's path in front."""
-
-    def __init__(self, target, prefix):
-        self.target, self.prefix = target, prefix
-
-    def append(self, text):
-        self.target.append(self.prefix + text)
-
-    def __bool__(self):
-        return False
 
 
 @dataclasses.dataclass(frozen=True)

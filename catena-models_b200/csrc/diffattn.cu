@@ -1,0 +1,491 @@
+// Difference-of-two-maps attention over a paged cache, with the short causal taps and the partial
+// rotation that come between its projections and its scores.
+//
+//   taps      y_t[c] = sum_j w[c][j] * u_(t - K + 1 + j)[c],  u = projection + bias, zeros before position 0;
+//             the last K - 1 values of u of every sequence are its state (float), so a step may begin anywhere
+//   rotation  of the leading `rot` channels of every vector of `sub` channels of q and k: channel i against
+//             channel i + rot/2, angle = float(position) * rate[i], sine and cosine times `mag`
+//   cache     a key/value head g holds, per position, a key row [map 1 | map 2] of 2 D channels and a value
+//             row of DV channels, each in an entry of HDC channels of this layer's pages
+//   scores    two maps per query head over the same values: s_m = (q_m . k_m) * scale, m = 1, 2; a key at
+//             position j is visible to a query at position i when j <= i and (i - j < window or j < keep;
+//             window <= 0: every j <= i); softmax per map in float
+//   output    o = a_1 - lambda * a_2;  o <- o / sqrt(mean(o^2) + eps) * out_scale * sigmoid(gate)
+//
+// Keys and values of the step are written to the cache before the scores are formed, and every key is
+// read from there, whatever the kind of step: whole prompts, portions and single tokens run the same
+// code.  (The cache keeps every position: a window with kept first tokens is not a ring.)
+// Rows whose tok_seq is negative are padding: they touch nothing.
+#include "common.cuh"
+#include <math.h>
+
+struct TapRotArgs {
+    const void* proj;            // [T][ldp] activations: q | k | v channels from column 0 on
+    long long ldp;
+    const float* bias;           // [C] or null
+    const float* taps;           // [C][K]
+    float* state;                // [slots][state_stride]: (K - 1) rows of C channels, oldest first
+    long long state_stride;
+    void* q_out;                 // [T][ldq] activations: the queries after taps and rotation
+    long long ldq;
+    void* pool;                  // this layer's pages [2][pages][G][PAGE_TOKENS][HDC], or null when KC = VC = 0
+    long long pages;
+    const int* ptab;
+    long long ptab_stride;
+    const float* rate;           // [rot / 2], or null for no rotation
+    float mag;
+    const int *tok_seq, *tok_pos, *seq_start, *seq_pos0, *seq_slot;
+    int T, B, QC, KC, VC, K, sub, rot, G, KW, DV, HDC;
+    int one_token_each;          // every sequence brings one token: the state moves on in the same launch
+};
+
+#define TR_THREADS 128
+#define TR_MAXK CM_MAX_CONV_TAPS
+
+template <typename T>
+__device__ __forceinline__ float tap_sum(const TapRotArgs& a, int c, int t, int pos, int p0, const float* st) {
+    const int C = a.QC + a.KC + a.VC, K = a.K;
+    const float* w = a.taps + (long long)c * K;
+    const float bias = a.bias ? a.bias[c] : 0.f;
+    float y = 0.f;
+    for (int j = 0; j < K; ++j) {
+        const int s = pos - K + 1 + j;                    // the position this tap reads
+        float u = 0.f;
+        if (s >= p0) u = to_f32(((const T*)a.proj)[(long long)(t - (pos - s)) * a.ldp + c]) + bias;
+        else if (s >= 0) u = st[(long long)(s - (p0 - (K - 1))) * C + c];
+        y = fmaf(w[j], u, y);
+    }
+    return y;
+}
+
+// One block per token; threads stride the channels.
+template <typename T>
+__global__ void __launch_bounds__(TR_THREADS)
+tap_rotate_store_kernel(const TapRotArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int b = a.tok_seq[t];
+    if (b < 0) return;
+    const int pos = a.tok_pos[t], p0 = a.seq_pos0[b];
+    const int C = a.QC + a.KC + a.VC, K = a.K;
+    float* st = a.state + (long long)a.seq_slot[b] * a.state_stride;
+    int page = 0;
+    const int row = pos % PAGE_TOKENS;
+    if (a.pool) page = a.ptab[(long long)a.seq_slot[b] * a.ptab_stride + pos / PAGE_TOKENS];
+    const int half = a.rot >> 1;
+    for (int c = threadIdx.x; c < C; c += TR_THREADS) {
+        float y = tap_sum<T>(a, c, t, pos, p0, st);
+        const int cr = c < a.QC ? c : c - a.QC;           // channel within q, or within k | v
+        if (c < a.QC + a.KC && a.rate) {
+            const int e = cr % a.sub;
+            if (e < a.rot) {
+                const bool low = e < half;
+                const float other = tap_sum<T>(a, low ? c + half : c - half, t, pos, p0, st);
+                float sn, cs;
+                sincosf((float)pos * a.rate[low ? e : e - half], &sn, &cs);
+                sn *= a.mag;
+                cs *= a.mag;
+                y = low ? y * cs - other * sn : y * cs + other * sn;
+            }
+        }
+        if (c < a.QC) {
+            ((T*)a.q_out)[(long long)t * a.ldq + c] = from_f32<T>(y);
+        } else if (cr < a.KC) {
+            const int g = cr / a.KW, off = cr - g * a.KW;
+            kv_tile((T*)a.pool, 0, a.pages, page, g, a.G, a.HDC)[(long long)row * a.HDC + off] = from_f32<T>(y);
+        } else {
+            const int cv = cr - a.KC, g = cv / a.DV, off = cv - g * a.DV;
+            kv_tile((T*)a.pool, 1, a.pages, page, g, a.G, a.HDC)[(long long)row * a.HDC + off] = from_f32<T>(y);
+        }
+    }
+    if (!a.one_token_each || K < 2) return;
+    // a single token: every read of the state above came from this block; each channel's column then moves on by one
+    __syncthreads();
+    for (int c = threadIdx.x; c < C; c += TR_THREADS) {
+        for (int i = 0; i + 1 < K - 1; ++i) st[(long long)i * C + c] = st[(long long)(i + 1) * C + c];
+        st[(long long)(K - 2) * C + c] = to_f32(((const T*)a.proj)[(long long)t * a.ldp + c]) + (a.bias ? a.bias[c] : 0.f);
+    }
+}
+
+// The state after a step of several tokens: one thread per (sequence, channel) gathers the K - 1 last values
+// (from the step's rows, or from the old state where the step was shorter), then stores them.
+template <typename T>
+__global__ void __launch_bounds__(TR_THREADS)
+tap_state_kernel(const TapRotArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    const int b = blockIdx.y;
+    const int c = blockIdx.x * TR_THREADS + threadIdx.x;
+    const int C = a.QC + a.KC + a.VC, K = a.K;
+    if (c >= C) return;
+    const int s0 = a.seq_start[b], n = a.seq_start[b + 1] - s0;
+    if (n <= 0) return;
+    const int p0 = a.seq_pos0[b], end = p0 + n;
+    float* st = a.state + (long long)a.seq_slot[b] * a.state_stride;
+    const float bias = a.bias ? a.bias[c] : 0.f;
+    float keep[TR_MAXK];
+#pragma unroll
+    for (int i = 0; i < TR_MAXK; ++i) {
+        if (i >= K - 1) break;
+        const int s = end - (K - 1) + i;
+        float u = 0.f;
+        if (s >= p0) u = to_f32(((const T*)a.proj)[(long long)(s0 + s - p0) * a.ldp + c]) + bias;
+        else if (s >= 0) u = st[(long long)(s - (p0 - (K - 1))) * C + c];
+        keep[i] = u;
+    }
+#pragma unroll
+    for (int i = 0; i < TR_MAXK; ++i) {
+        if (i >= K - 1) break;
+        st[(long long)i * C + c] = keep[i];
+    }
+}
+
+extern "C" int cm_tap_rotate_store(int dt, const TapRotArgs* args, cudaStream_t st) {
+    TapRotArgs a = *args;
+    if (a.T <= 0) return CM_OK;
+    const int C = a.QC + a.KC + a.VC;
+    if (a.K < 1 || a.K > TR_MAXK) CM_REFUSE("tap_rotate_store: %d taps (1 to %d)", a.K, TR_MAXK);
+    if (a.rate && (a.rot % 2 || a.rot > a.sub || a.sub <= 0 || a.QC % a.sub || a.KC % a.sub))
+        CM_REFUSE("tap_rotate_store: %d turned channels in vectors of %d", a.rot, a.sub);
+    if ((a.KC || a.VC) && (!a.pool || a.KW > a.HDC || a.DV > a.HDC || a.KC != a.G * a.KW || a.VC != a.G * a.DV))
+        CM_REFUSE("tap_rotate_store: %d key and %d value channels do not fit %d heads of %d", a.KC, a.VC, a.G, a.HDC);
+    if (a.state_stride < (long long)(a.K - 1) * C) CM_REFUSE("tap_rotate_store: a state row of %lld floats is too short", a.state_stride);
+    dim3 sgrid((C + TR_THREADS - 1) / TR_THREADS, a.B);
+    if (dt == DT_F32) {
+        cm_launch(tap_rotate_store_kernel<float>, a.T, TR_THREADS, 0, st, a);
+        CM_CHECK_LAUNCH();
+        if (!a.one_token_each && a.K > 1) cm_launch(tap_state_kernel<float>, sgrid, TR_THREADS, 0, st, a);
+    } else if (dt == DT_BF16) {
+        cm_launch(tap_rotate_store_kernel<bf16>, a.T, TR_THREADS, 0, st, a);
+        CM_CHECK_LAUNCH();
+        if (!a.one_token_each && a.K > 1) cm_launch(tap_state_kernel<bf16>, sgrid, TR_THREADS, 0, st, a);
+    } else
+        return CM_ERR_DTYPE;
+    CM_CHECK_LAUNCH();
+    return CM_OK;
+}
+
+// ================================================================================ the two maps
+struct DiffAttnArgs {
+    void* ctx;                   // [T][ldc]: H heads of DV channels
+    long long ldc;
+    const void* q;               // [T][ldq]: H heads of [map 1 | map 2], D channels each
+    long long ldq;
+    const void* gate;            // [T][ldg]: a logit per head, or null
+    long long ldg;
+    const void* pool;
+    long long pages;
+    const int* ptab;
+    long long ptab_stride;
+    const int *tok_seq, *tok_pos, *seq_start, *seq_pos0, *seq_slot;
+    int T, B, H, G, D, DV, HDC, window, keep;
+    float scale, lambda, out_scale, eps;
+};
+
+__device__ __forceinline__ bool da_visible(int kpos, int qpos, int window, int keep) {
+    return kpos <= qpos && (window <= 0 || qpos - kpos < window || kpos < keep);
+}
+
+// what a query's two finished maps become: a lane holds channels lane, lane + 32, ... of both
+template <typename T, int NJ>
+__device__ __forceinline__ void da_finish(const DiffAttnArgs& a, long long t, int h, const float* acc1, const float* acc2,
+                                          float l1, float l2) {
+    const int lane = threadIdx.x & 31;
+    const float i1 = 1.f / l1, i2 = 1.f / l2;
+    float o[NJ], ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+        o[j] = (lane + 32 * j < a.DV) ? acc1[j] * i1 - a.lambda * (acc2[j] * i2) : 0.f;
+        ss = fmaf(o[j], o[j], ss);
+    }
+    ss = warp_sum(ss);
+    float f = a.out_scale / sqrtf(ss / (float)a.DV + a.eps);
+    if (a.gate) f *= sigmoid_f32(to_f32(((const T*)a.gate)[t * a.ldg + h]));
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+        const int d = lane + 32 * j;
+        if (d < a.DV) ((T*)a.ctx)[t * a.ldc + (long long)h * a.DV + d] = from_f32<T>(o[j] * f);
+    }
+}
+
+// -------------------------------------------------------------------------------- many rows a sequence
+// One block = DA_BQ queries of one head of one sequence (warp w owns queries 4w .. 4w + 3); keys come in
+// tiles of 32 from the cache: the tiles that hold kept first tokens, then those the block's windows reach.
+// A lane is a key for the scores and a set of channels for the value sums.
+#define DA_BQ 32
+#define DA_BK 32
+#define DA_QPW 4
+#define DA_THREADS 256
+
+template <typename T, int NJ>
+__global__ void __launch_bounds__(DA_THREADS)
+diff_attn_tile_kernel(const DiffAttnArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float smem[];
+    const int D2 = 2 * a.D, ldk = D2 + 1, DV = a.DV;
+    float* Qs = smem;                            // [DA_BQ][2D + 1]
+    float* Ks = Qs + DA_BQ * ldk;                // [DA_BK][2D + 1]
+    float* Vs = Ks + DA_BK * ldk;                // [DA_BK][DV]
+    float* Ps = Vs + DA_BK * DV;                 // [2][DA_BQ][DA_BK + 1]
+    const int b = blockIdx.z, h = blockIdx.y, g = h / (a.H / a.G);
+    const int s0 = a.seq_start[b], n_new = a.seq_start[b + 1] - s0;
+    const int p0 = a.seq_pos0[b], len = p0 + n_new;
+    const int q0 = p0 + blockIdx.x * DA_BQ;
+    if (q0 >= len) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nq = min(DA_BQ, len - q0), q_last = q0 + nq - 1;
+    const int* prow = a.ptab + (long long)a.seq_slot[b] * a.ptab_stride;
+    for (int e = threadIdx.x; e < DA_BQ * D2; e += DA_THREADS) {
+        const int r = e / D2, d = e - r * D2;
+        Qs[r * ldk + d] = r < nq ? to_f32(((const T*)a.q)[(long long)(s0 + q0 - p0 + r) * a.ldq + (long long)h * D2 + d]) : 0.f;
+    }
+    float m1[DA_QPW], l1[DA_QPW], m2[DA_QPW], l2[DA_QPW], acc1[DA_QPW][NJ], acc2[DA_QPW][NJ];
+#pragma unroll
+    for (int i = 0; i < DA_QPW; ++i) {
+        m1[i] = m2[i] = -INFINITY;
+        l1[i] = l2[i] = 0.f;
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) acc1[i][j] = acc2[i][j] = 0.f;
+    }
+    // tiles [0, kept_end) hold kept first tokens; the windows begin in tile win_tile
+    const int win_first = a.window > 0 ? max(0, q0 - a.window + 1) : 0;
+    const int kept_end = a.window > 0 ? min(a.keep, q_last + 1) : 0;
+    const int win_k0 = win_first / DA_BK * DA_BK;
+    for (int k0 = 0; k0 <= q_last; k0 += DA_BK) {
+        if (k0 >= kept_end && k0 < win_k0) {                 // nothing of this tile is seen: on to the windows
+            k0 = win_k0 - DA_BK;
+            continue;
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < DA_BK * D2; e += DA_THREADS) {
+            const int r = e / D2, d = e - r * D2, kp = k0 + r;
+            float x = 0.f;
+            if (kp < len)
+                x = to_f32(kv_tile((const T*)a.pool, 0, a.pages, prow[kp / PAGE_TOKENS], g, a.G, a.HDC)[(long long)(kp % PAGE_TOKENS) * a.HDC + d]);
+            Ks[r * ldk + d] = x;
+        }
+        for (int e = threadIdx.x; e < DA_BK * DV; e += DA_THREADS) {
+            const int r = e / DV, d = e - r * DV, kp = k0 + r;
+            float x = 0.f;
+            if (kp < len)
+                x = to_f32(kv_tile((const T*)a.pool, 1, a.pages, prow[kp / PAGE_TOKENS], g, a.G, a.HDC)[(long long)(kp % PAGE_TOKENS) * a.HDC + d]);
+            Vs[r * DV + d] = x;
+        }
+        __syncthreads();
+        const int kpos = k0 + lane;
+        const float* kr = Ks + lane * ldk;
+#pragma unroll
+        for (int i = 0; i < DA_QPW; ++i) {
+            const int qi = warp * DA_QPW + i, qpos = q0 + qi;
+            const float* qr = Qs + qi * ldk;
+            float s1 = 0.f, s2 = 0.f;
+            for (int d = 0; d < a.D; ++d) {
+                s1 = fmaf(qr[d], kr[d], s1);
+                s2 = fmaf(qr[a.D + d], kr[a.D + d], s2);
+            }
+            const bool vis = qi < nq && kpos < len && da_visible(kpos, qpos, a.window, a.keep);
+            s1 = vis ? s1 * a.scale : -INFINITY;
+            s2 = vis ? s2 * a.scale : -INFINITY;
+            const float x1 = fmaxf(m1[i], warp_max(s1)), x2 = fmaxf(m2[i], warp_max(s2));
+            float p1 = 0.f, p2 = 0.f, f1 = 1.f, f2 = 1.f;
+            if (x1 != -INFINITY) {                   // both maps see the same keys
+                p1 = vis ? expf(s1 - x1) : 0.f;
+                p2 = vis ? expf(s2 - x2) : 0.f;
+                f1 = expf(m1[i] - x1);
+                f2 = expf(m2[i] - x2);
+            }
+            l1[i] = l1[i] * f1 + warp_sum(p1);
+            l2[i] = l2[i] * f2 + warp_sum(p2);
+            m1[i] = x1;
+            m2[i] = x2;
+#pragma unroll
+            for (int j = 0; j < NJ; ++j) {
+                acc1[i][j] *= f1;
+                acc2[i][j] *= f2;
+            }
+            Ps[qi * (DA_BK + 1) + lane] = p1;
+            Ps[(DA_BQ + qi) * (DA_BK + 1) + lane] = p2;
+        }
+        __syncwarp();
+        for (int kk = 0; kk < DA_BK; ++kk) {
+            float vv[NJ];
+#pragma unroll
+            for (int j = 0; j < NJ; ++j) vv[j] = (lane + 32 * j < DV) ? Vs[kk * DV + lane + 32 * j] : 0.f;
+#pragma unroll
+            for (int i = 0; i < DA_QPW; ++i) {
+                const float p1 = Ps[(warp * DA_QPW + i) * (DA_BK + 1) + kk];
+                const float p2 = Ps[(DA_BQ + warp * DA_QPW + i) * (DA_BK + 1) + kk];
+#pragma unroll
+                for (int j = 0; j < NJ; ++j) {
+                    acc1[i][j] = fmaf(p1, vv[j], acc1[i][j]);
+                    acc2[i][j] = fmaf(p2, vv[j], acc2[i][j]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < DA_QPW; ++i) {
+        const int qi = warp * DA_QPW + i;
+        if (qi < nq) da_finish<T, NJ>(a, (long long)s0 + q0 - p0 + qi, h, acc1[i], acc2[i], l1[i], l2[i]);
+    }
+}
+
+// -------------------------------------------------------------------------------- a row at a time
+// One block = one row (token) and head; the warps take the visible tiles of 32 keys in turns, each with
+// running maxima and sums of its own, which are merged in warp order.  A lane is a key for the scores
+// (its key's row read straight from the cache) and a set of channels for the value sums.
+#define DR_WARPS 8
+
+template <typename T, int NJ>
+__global__ void __launch_bounds__(DR_WARPS * 32)
+diff_attn_row_kernel(const DiffAttnArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float smem[];
+    const int D2 = 2 * a.D, DV = a.DV;
+    float* Qs = smem;                            // [2D]
+    float* Ms = Qs + D2;                         // [DR_WARPS][4]: m1, l1, m2, l2
+    float* As = Ms + DR_WARPS * 4;               // [DR_WARPS][2][DV]
+    const long long t = blockIdx.y;
+    const int h = blockIdx.x, g = h / (a.H / a.G);
+    const int b = a.tok_seq[t];
+    if (b < 0) return;
+    const int qpos = a.tok_pos[t];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int* prow = a.ptab + (long long)a.seq_slot[b] * a.ptab_stride;
+    for (int d = threadIdx.x; d < D2; d += DR_WARPS * 32) Qs[d] = to_f32(((const T*)a.q)[t * a.ldq + (long long)h * D2 + d]);
+    __syncthreads();
+    float m1 = -INFINITY, m2 = -INFINITY, l1 = 0.f, l2 = 0.f, acc1[NJ], acc2[NJ];
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) acc1[j] = acc2[j] = 0.f;
+    const int last_tile = qpos / 32;
+    const int kept_tiles = a.window > 0 ? min((min(a.keep, qpos + 1) + 31) / 32, last_tile + 1) : 0;
+    const int win_tile = a.window > 0 ? max(kept_tiles, max(0, qpos - a.window + 1) / 32) : 0;
+    const int n_tiles = kept_tiles + (last_tile - win_tile + 1);
+    for (int idx = warp; idx < n_tiles; idx += DR_WARPS) {
+        const int tile = idx < kept_tiles ? idx : win_tile + idx - kept_tiles;
+        const int kpos = tile * 32 + lane;
+        const bool vis = da_visible(kpos, qpos, a.window, a.keep);
+        const int page = kpos <= qpos ? prow[kpos / PAGE_TOKENS] : 0;
+        float s1 = 0.f, s2 = 0.f;
+        if (vis) {
+            const T* kr = kv_tile((const T*)a.pool, 0, a.pages, page, g, a.G, a.HDC) + (long long)(kpos % PAGE_TOKENS) * a.HDC;
+            for (int d = 0; d < a.D; ++d) {
+                s1 = fmaf(Qs[d], to_f32(kr[d]), s1);
+                s2 = fmaf(Qs[a.D + d], to_f32(kr[a.D + d]), s2);
+            }
+        }
+        s1 = vis ? s1 * a.scale : -INFINITY;
+        s2 = vis ? s2 * a.scale : -INFINITY;
+        const float x1 = fmaxf(m1, warp_max(s1)), x2 = fmaxf(m2, warp_max(s2));
+        if (x1 == -INFINITY) continue;           // no key of this tile is seen (uniform over the warp)
+        const float p1 = vis ? expf(s1 - x1) : 0.f, p2 = vis ? expf(s2 - x2) : 0.f;
+        const float f1 = expf(m1 - x1), f2 = expf(m2 - x2);
+        l1 = l1 * f1 + warp_sum(p1);
+        l2 = l2 * f2 + warp_sum(p2);
+        m1 = x1;
+        m2 = x2;
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) {
+            acc1[j] *= f1;
+            acc2[j] *= f2;
+        }
+        const unsigned seen = __ballot_sync(0xffffffffu, vis);
+        for (int kk = 0; kk < 32; ++kk) {
+            if (!((seen >> kk) & 1u)) continue;  // an unseen key's values may never have been written
+            const float q1 = __shfl_sync(0xffffffffu, p1, kk), q2 = __shfl_sync(0xffffffffu, p2, kk);
+            const int kp = tile * 32 + kk;
+            const int pg = __shfl_sync(0xffffffffu, page, kk);
+            const T* vr = kv_tile((const T*)a.pool, 1, a.pages, pg, g, a.G, a.HDC) + (long long)(kp % PAGE_TOKENS) * a.HDC;
+#pragma unroll
+            for (int j = 0; j < NJ; ++j) {
+                const int d = lane + 32 * j;
+                const float v = d < DV ? to_f32(vr[d]) : 0.f;
+                acc1[j] = fmaf(q1, v, acc1[j]);
+                acc2[j] = fmaf(q2, v, acc2[j]);
+            }
+        }
+    }
+    if (lane == 0) {
+        Ms[warp * 4] = m1;
+        Ms[warp * 4 + 1] = l1;
+        Ms[warp * 4 + 2] = m2;
+        Ms[warp * 4 + 3] = l2;
+    }
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+        const int d = lane + 32 * j;
+        if (d < DV) {
+            As[(warp * 2) * DV + d] = acc1[j];
+            As[(warp * 2 + 1) * DV + d] = acc2[j];
+        }
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    float M1 = -INFINITY, M2 = -INFINITY;
+    for (int w = 0; w < DR_WARPS; ++w) {
+        M1 = fmaxf(M1, Ms[w * 4]);
+        M2 = fmaxf(M2, Ms[w * 4 + 2]);
+    }
+    float L1 = 0.f, L2 = 0.f, o1[NJ], o2[NJ];
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) o1[j] = o2[j] = 0.f;
+    for (int w = 0; w < DR_WARPS; ++w) {
+        if (Ms[w * 4] == -INFINITY) continue;    // a warp that saw no tile
+        const float f1 = expf(Ms[w * 4] - M1), f2 = expf(Ms[w * 4 + 2] - M2);
+        L1 = fmaf(Ms[w * 4 + 1], f1, L1);
+        L2 = fmaf(Ms[w * 4 + 3], f2, L2);
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) {
+            const int d = lane + 32 * j;
+            if (d < DV) {
+                o1[j] = fmaf(As[(w * 2) * DV + d], f1, o1[j]);
+                o2[j] = fmaf(As[(w * 2 + 1) * DV + d], f2, o2[j]);
+            }
+        }
+    }
+    da_finish<T, NJ>(a, t, h, o1, o2, L1, L2);
+}
+
+template <typename T, int NJ>
+static int da_launch(const DiffAttnArgs& a, int rows_form, int max_len, cudaStream_t st) {
+    if (rows_form) {
+        const size_t smem = ((size_t)2 * a.D + DR_WARPS * 4 + (size_t)DR_WARPS * 2 * a.DV) * sizeof(float);
+        if (smem > 48 * 1024) cudaFuncSetAttribute(diff_attn_row_kernel<T, NJ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cm_launch(diff_attn_row_kernel<T, NJ>, dim3(a.H, a.T), DR_WARPS * 32, smem, st, a);
+    } else {
+        const size_t smem = ((size_t)(DA_BQ + DA_BK) * (2 * a.D + 1) + (size_t)DA_BK * a.DV + 2 * DA_BQ * (DA_BK + 1)) * sizeof(float);
+        if (smem > 200 * 1024) CM_REFUSE("diff_attn: heads of 2 x %d and %d channels do not fit shared memory", a.D, a.DV);
+        if (smem > 48 * 1024) cudaFuncSetAttribute(diff_attn_tile_kernel<T, NJ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cm_launch(diff_attn_tile_kernel<T, NJ>, dim3((max_len + DA_BQ - 1) / DA_BQ, a.H, a.B), DA_THREADS, smem, st, a);
+    }
+    CM_CHECK_LAUNCH();
+    return CM_OK;
+}
+
+// rows_form: one block per row and head (steps of one or few tokens a sequence); else tiles of 32 queries,
+// launched for sequences of up to max_len new tokens.
+extern "C" int cm_diff_attn(int dt, const DiffAttnArgs* args, int rows_form, int max_len, cudaStream_t st) {
+    const DiffAttnArgs a = *args;
+    if (a.T <= 0 || a.B <= 0) return CM_OK;
+    if (a.D <= 0 || a.DV <= 0 || a.DV > CM_MAX_HEAD_DIM || 2 * a.D > a.HDC || a.DV > a.HDC)
+        CM_REFUSE("diff_attn: heads of 2 x %d key and %d value channels in entries of %d (values up to %d)", a.D, a.DV, a.HDC, CM_MAX_HEAD_DIM);
+    if (a.G <= 0 || a.H % a.G) CM_REFUSE("diff_attn: %d query heads over %d key heads", a.H, a.G);
+    if (!rows_form && max_len <= 0) return CM_OK;
+    const int nj = (a.DV + 31) / 32;
+#define DA_DISPATCH(TT)                                                     \
+    do {                                                                    \
+        if (nj <= 1) return da_launch<TT, 1>(a, rows_form, max_len, st);    \
+        if (nj == 2) return da_launch<TT, 2>(a, rows_form, max_len, st);    \
+        if (nj == 3) return da_launch<TT, 3>(a, rows_form, max_len, st);    \
+        if (nj == 4) return da_launch<TT, 4>(a, rows_form, max_len, st);    \
+        if (nj <= 6) return da_launch<TT, 6>(a, rows_form, max_len, st);    \
+        return da_launch<TT, 8>(a, rows_form, max_len, st);                 \
+    } while (0)
+    if (dt == DT_F32) DA_DISPATCH(float);
+    if (dt == DT_BF16) DA_DISPATCH(bf16);
+#undef DA_DISPATCH
+    return CM_ERR_DTYPE;
+}

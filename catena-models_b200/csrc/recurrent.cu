@@ -4,6 +4,8 @@
 //                  (per-channel decay w_t in (0, 1) that depends on the token, bonus u for the present token)
 //   matrix memory  m' = max(f + m, i) ;  S <- e^(f + m - m') S + e^(i - m') k v^T ;  n likewise with k alone ;
 //                  o = S^T q / (max(|n . q|, e^(-m')) + 1e-6)         (log-domain gates i, f with a running maximum m)
+//   constant decay S <- w S + k v^T ;  o = S^T q                      (one decay w in (0, 1] per head, the same for
+//                  every token; q, k and v may pass through silu on their way in: lightning attention)
 //
 // followed by the unit norm of each head's output, the channel weights and the output gate.  State, gates,
 // decays and all sums are float whatever the activation type.  The state lives in per-slot rows of a float
@@ -235,6 +237,8 @@ struct ScanArgs {
     float q_scale, eps;
     float* raw;                       // [rows][H * DV] float: the heads' outputs before norm and gate
     long long rows;
+    int qkv_act;                      // MODE 2: 1 = q, k and v pass through silu (in float) as they are staged
+    int norm_all_heads;               // 1: the unit norm runs over all heads of a row together, not head by head
 };
 
 #define SCAN_THREADS 128
@@ -257,7 +261,7 @@ __device__ __forceinline__ void load_run(const float* p, float* out) {
     }
 }
 
-// MODE 0: decay mix.  MODE 1: matrix memory.  A block owns some columns of one head's S for one sequence and
+// MODE 0: decay mix.  MODE 1: matrix memory.  MODE 2: constant decay per head (a.decay [H]).  A block owns some columns of one head's S for one sequence and
 // walks the sequence's rows of the step in order.  Thread (column c, part ks) keeps S[i][c] for the RPT key
 // channels i = ks * RPT ... in registers.  For the matrix memory the block's last column is the normaliser n: it
 // is the column of S whose value channel is constantly one (n <- a n + b k, and its output is n . q), so it needs
@@ -309,13 +313,15 @@ matrix_scan_kernel(const ScanArgs a, int TB) {
     const T* K = (const T*)a.k + (long long)hd * D;
     const T* V = (const T*)a.v + (long long)hd * DV + (long long)cb * real;
     const float* Wd = a.decay + (MODE == 0 ? (long long)hd * D : 0);
+    const float w_head = MODE == 2 ? a.decay[hd] : 1.f;
+    const bool act = MODE == 2 && a.qkv_act;
     const long long ldw = MODE == 0 ? (long long)H * D : 2LL * H;
     float* R = a.raw + (long long)hd * DV + (long long)cb * real;
     const long long ldr = (long long)H * DV;
     const int n_cols = max(0, min(real, DV - cb * real));
     // 16-byte accesses to q, k and the decay: heads of a multiple of 8 channels in rows and buffers aligned to match
-    const bool vec8 = D % 8 == 0 && a.ldq % 8 == 0 && a.ldk % 8 == 0 && (ldw % 8 == 0 || MODE == 1) &&
-                      (((uintptr_t)a.q | (uintptr_t)a.k) & 15) == 0 && (MODE == 1 || ((uintptr_t)a.decay & 31) == 0);
+    const bool vec8 = D % 8 == 0 && a.ldq % 8 == 0 && a.ldk % 8 == 0 && (ldw % 8 == 0 || MODE != 0) &&
+                      (((uintptr_t)a.q | (uintptr_t)a.k) & 15) == 0 && (MODE != 0 || ((uintptr_t)a.decay & 31) == 0);
     // channels past D of a staged row are read by the last part's vector accesses: they hold zeros
     for (int e = threadIdx.x; e < TB * (Dp - D); e += SCAN_THREADS) {
         const int tt = e / (Dp - D), i = D + e - tt * (Dp - D);
@@ -346,6 +352,13 @@ matrix_scan_kernel(const ScanArgs a, int TB) {
                     const int e = e0 + u * SCAN_THREADS;
                     if (e < n8) {
                         const int tt = e / D8, i = (e - tt * D8) * 8;
+                        if (act) {
+#pragma unroll
+                            for (int x = 0; x < 8; ++x) {
+                                fq[u][x] *= sigmoid_f32(fq[u][x]);
+                                fk[u][x] *= sigmoid_f32(fk[u][x]);
+                            }
+                        }
 #pragma unroll
                         for (int x = 0; x < 8; ++x) fq[u][x] *= a.q_scale;
                         store8f<float>(sq + (size_t)tt * Dp + i, fq[u]);
@@ -357,14 +370,21 @@ matrix_scan_kernel(const ScanArgs a, int TB) {
         } else {
             for (int e = threadIdx.x; e < nt * D; e += SCAN_THREADS) {
                 const int tt = e / D, i = e - tt * D;
-                sq[(size_t)tt * Dp + i] = to_f32(Q[(t0 + tt) * a.ldq + i]) * a.q_scale;
-                sk[(size_t)tt * Dp + i] = to_f32(K[(t0 + tt) * a.ldk + i]);
+                float fq = to_f32(Q[(t0 + tt) * a.ldq + i]), fk = to_f32(K[(t0 + tt) * a.ldk + i]);
+                if (act) {
+                    fq *= sigmoid_f32(fq);
+                    fk *= sigmoid_f32(fk);
+                }
+                sq[(size_t)tt * Dp + i] = fq * a.q_scale;
+                sk[(size_t)tt * Dp + i] = fk;
                 if (MODE == 0) sw[(size_t)tt * Dp + i] = Wd[(t0 + tt) * ldw + i];
             }
         }
         for (int e = threadIdx.x; e < nt * cols; e += SCAN_THREADS) {
             const int tt = e / cols, cc = e - tt * cols;
-            sv[e] = (MODE == 1 && cc == real) ? 1.f : (cc < n_cols ? to_f32(V[(t0 + tt) * a.ldv + cc]) : 0.f);
+            float fv = (MODE == 1 && cc == real) ? 1.f : (cc < n_cols ? to_f32(V[(t0 + tt) * a.ldv + cc]) : 0.f);
+            if (act) fv *= sigmoid_f32(fv);
+            sv[e] = fv;
         }
         if (MODE == 1 && warp == 0) {
             // the gates of the group: lane tt fetches row tt's pair; the running maximum is a chain over the rows, which
@@ -398,7 +418,7 @@ matrix_scan_kernel(const ScanArgs a, int TB) {
             load_run<RPT>(sk + (size_t)tt * Dp + i0, k);
             if (MODE == 0) load_run<RPT>(sw + (size_t)tt * Dp + i0, w);
             const float vj = sv[tt * cols + c];
-            const float af = MODE == 1 ? sg[4 * tt] : 1.f, bv = MODE == 1 ? sg[4 * tt + 1] * vj : vj;
+            const float af = MODE == 1 ? sg[4 * tt] : w_head, bv = MODE == 1 ? sg[4 * tt + 1] * vj : vj;
             float acc = 0.f;
 #pragma unroll
             for (int it = 0; it < RPT; ++it) {
@@ -473,12 +493,14 @@ head_norm_gate_kernel(const ScanArgs a) {
     }
 }
 
-// mode 0: decay mix, mode 1: matrix memory.  B sequences; rows of the step are found through seq_start.
+// mode 0: decay mix, mode 1: matrix memory, mode 2: constant decay per head.  B sequences; rows of the step are found
+// through seq_start.
 extern "C" int cm_matrix_scan(int dt, int mode, const ScanArgs* args, int B, cudaStream_t st) {
     ScanArgs a = *args;
     if (B <= 0 || a.rows <= 0) return CM_OK;
     if (a.D <= 0 || a.DV <= 0 || a.D > 1024) CM_REFUSE("matrix_scan: head sizes %d x %d (keys up to 1024)", a.D, a.DV);
     if (!a.raw) CM_REFUSE("matrix_scan: the float buffer for the heads' raw outputs is missing");
+    if (mode < 0 || mode > 2) CM_REFUSE("matrix_scan: mode %d", mode);
     // Channels per thread (a power of two from 2 to 32) and parts per column (a power of two up to 32): as many
     // channels as leave the grid with a block per SM.  The walk is bound by its latency per row, not by arithmetic,
     // so what counts is how many SMs walk at once (measured on B200, 2,048 rows, one sequence, 8 heads of 64 x 128 /
@@ -502,7 +524,13 @@ extern "C" int cm_matrix_scan(int dt, int mode, const ScanArgs* args, int B, cud
     tb = tb < 1 ? 1 : (tb > SCAN_MAX_ROWS ? SCAN_MAX_ROWS : tb);
     const size_t smem = (size_t)tb * row_floats * sizeof(float);
     dim3 grid(a.H, (a.DV + real - 1) / real, B);
-    dim3 egrid((unsigned)((a.rows * a.H + 3) / 4));
+    // the norm over all heads of a row together is the norm of one head that spans the row
+    ScanArgs n = a;
+    if (a.norm_all_heads) {
+        n.DV = a.H * a.DV;
+        n.H = 1;
+    }
+    dim3 egrid((unsigned)((n.rows * n.H + 3) / 4));
 #define SCAN_LAUNCH(TT, M, R)                                                                                    \
     do {                                                                                                         \
         if (smem > 48 * 1024)                                                                                    \
@@ -517,10 +545,12 @@ extern "C" int cm_matrix_scan(int dt, int mode, const ScanArgs* args, int B, cud
         else if (rpt == 16) SCAN_LAUNCH(TT, M, 16); \
         else SCAN_LAUNCH(TT, M, 32);                \
     } while (0)
-    if (dt == DT_F32 && mode == 0) { SCAN_RPT(float, 0); CM_CHECK_LAUNCH(); cm_launch(head_norm_gate_kernel<float, 0>, egrid, 128, 0, st, a); }
-    else if (dt == DT_F32 && mode == 1) { SCAN_RPT(float, 1); CM_CHECK_LAUNCH(); cm_launch(head_norm_gate_kernel<float, 1>, egrid, 128, 0, st, a); }
-    else if (dt == DT_BF16 && mode == 0) { SCAN_RPT(bf16, 0); CM_CHECK_LAUNCH(); cm_launch(head_norm_gate_kernel<bf16, 0>, egrid, 128, 0, st, a); }
-    else if (dt == DT_BF16 && mode == 1) { SCAN_RPT(bf16, 1); CM_CHECK_LAUNCH(); cm_launch(head_norm_gate_kernel<bf16, 1>, egrid, 128, 0, st, a); }
+    if (dt == DT_F32 && mode == 0) { SCAN_RPT(float, 0); CM_CHECK_LAUNCH(); cm_launch(head_norm_gate_kernel<float, 0>, egrid, 128, 0, st, n); }
+    else if (dt == DT_F32 && mode == 1) { SCAN_RPT(float, 1); CM_CHECK_LAUNCH(); cm_launch(head_norm_gate_kernel<float, 1>, egrid, 128, 0, st, n); }
+    else if (dt == DT_BF16 && mode == 0) { SCAN_RPT(bf16, 0); CM_CHECK_LAUNCH(); cm_launch(head_norm_gate_kernel<bf16, 0>, egrid, 128, 0, st, n); }
+    else if (dt == DT_BF16 && mode == 1) { SCAN_RPT(bf16, 1); CM_CHECK_LAUNCH(); cm_launch(head_norm_gate_kernel<bf16, 1>, egrid, 128, 0, st, n); }
+    else if (dt == DT_F32 && mode == 2) { SCAN_RPT(float, 2); CM_CHECK_LAUNCH(); cm_launch(head_norm_gate_kernel<float, 1>, egrid, 128, 0, st, n); }
+    else if (dt == DT_BF16 && mode == 2) { SCAN_RPT(bf16, 2); CM_CHECK_LAUNCH(); cm_launch(head_norm_gate_kernel<bf16, 1>, egrid, 128, 0, st, n); }
     else return CM_ERR_DTYPE;
 #undef SCAN_RPT
 #undef SCAN_LAUNCH

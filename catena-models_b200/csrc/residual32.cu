@@ -3,6 +3,9 @@
 // the norm of whatever runs next, and the concatenation [x; x0] that a looped stack feeds to the
 // projection at the start of a pass.
 //
+// The norm is a root-mean-square norm (kind 0) or a dynamic tanh (kind 1: y = tanh(alpha x) * w + b, which takes
+// no statistics of the row; alpha is read from the device).
+//
 // A row is held in shared memory between the two passes over it (sum of squares, then scaling), so the
 // width is bounded by shared memory only.  All sums are float and run in a fixed order.
 #include "common.cuh"
@@ -29,15 +32,25 @@ __device__ __forceinline__ float term_at(const ResidualTerm& t, long long i) {
     return t.is_f32 ? reinterpret_cast<const float*>(t.p)[i] : to_f32(reinterpret_cast<const T*>(t.p)[i]);
 }
 
-// y = T((x * inv) * w), inv = 1 / sqrt(mean(x^2) + eps); x float.
+#define NORM_RMS 0
+#define NORM_DYT 1
+
+// y = T((x * inv) * w), inv = 1 / sqrt(mean(x^2) + eps); or T(tanh(alpha x) * w + b); x float.
 template <typename T>
 __global__ void __launch_bounds__(R32_THREADS)
-norm_f32in_kernel(T* __restrict__ y, const float* __restrict__ x, const float* __restrict__ w, int H, float eps) {
+norm_f32in_kernel(T* __restrict__ y, const float* __restrict__ x, const float* __restrict__ w, int H, float eps,
+                  int kind, const float* __restrict__ alpha, const float* __restrict__ shift) {
     extern __shared__ float row[];
     __shared__ float scratch[32];
     pdl_trigger();
     pdl_wait();
     const float* xr = x + (long long)blockIdx.x * H;
+    if (kind == NORM_DYT) {
+        const float al = alpha[0];
+        T* yd = y + (long long)blockIdx.x * H;
+        for (int c = threadIdx.x; c < H; c += R32_THREADS) yd[c] = from_f32<T>(fmaf(tanhf(al * xr[c]), w[c], shift[c]));
+        return;
+    }
     float ss = 0.f;
     for (int c = threadIdx.x; c < H; c += R32_THREADS) {
         const float v = xr[c];
@@ -55,7 +68,8 @@ norm_f32in_kernel(T* __restrict__ y, const float* __restrict__ x, const float* _
 template <typename T>
 __global__ void __launch_bounds__(R32_THREADS)
 residual_add_norm_kernel(float* __restrict__ h, T* __restrict__ n_out, ResidualTerms terms,
-                         const float* __restrict__ bias, const float* __restrict__ w, int H, float eps) {
+                         const float* __restrict__ bias, const float* __restrict__ w, int H, float eps,
+                         int kind, const float* __restrict__ alpha, const float* __restrict__ shift) {
     extern __shared__ float row[];
     __shared__ float scratch[32];
     pdl_trigger();
@@ -81,9 +95,14 @@ residual_add_norm_kernel(float* __restrict__ h, T* __restrict__ n_out, ResidualT
         ss += v * v;
     }
     if (!n_out) return;
+    T* nr = n_out + r * H;
+    if (kind == NORM_DYT) {                          // every thread reads back what it stored itself
+        const float al = alpha[0];
+        for (int c = threadIdx.x; c < H; c += R32_THREADS) nr[c] = from_f32<T>(fmaf(tanhf(al * row[c]), w[c], shift[c]));
+        return;
+    }
     ss = block_sum(ss, scratch);
     const float inv = 1.f / sqrtf(ss / (float)H + eps);
-    T* nr = n_out + r * H;
     for (int c = threadIdx.x; c < H; c += R32_THREADS) nr[c] = from_f32<T>((row[c] * inv) * w[c]);
 }
 
@@ -108,16 +127,17 @@ static int row_smem(int H, size_t* out) {
 }
 
 extern "C" int cm_norm_f32in(int dt, void* y, const float* x, const float* w, int rows, int H, float eps,
-                             cudaStream_t st) {
+                             int kind, const float* alpha, const float* shift, cudaStream_t st) {
     if (rows <= 0) return CM_OK;
+    if (kind == NORM_DYT && (!alpha || !shift)) CM_REFUSE("norm_f32in: a dynamic tanh needs its alpha and its shift");
     size_t smem;
     if (row_smem(H, &smem) != CM_OK) return CM_ERR_SHAPE;
     if (dt == DT_F32) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(norm_f32in_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cm_launch(norm_f32in_kernel<float>, rows, R32_THREADS, smem, st, (float*)y, x, w, H, eps);
+        cm_launch(norm_f32in_kernel<float>, rows, R32_THREADS, smem, st, (float*)y, x, w, H, eps, kind, alpha, shift);
     } else if (dt == DT_BF16) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(norm_f32in_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cm_launch(norm_f32in_kernel<bf16>, rows, R32_THREADS, smem, st, (bf16*)y, x, w, H, eps);
+        cm_launch(norm_f32in_kernel<bf16>, rows, R32_THREADS, smem, st, (bf16*)y, x, w, H, eps, kind, alpha, shift);
     } else
         return CM_ERR_DTYPE;
     CM_CHECK_LAUNCH();
@@ -127,10 +147,12 @@ extern "C" int cm_norm_f32in(int dt, void* y, const float* x, const float* w, in
 // terms: n_terms entries of (pointer, scale, pieces per row, stored as float?, index of the pieces or null) in parallel arrays.
 extern "C" int cm_residual_add_norm(int dt, float* h, void* n_out, int n_terms, const void* const* term_ptr,
                                     const float* term_scale, const int* term_per_row, const int* term_is_f32,
-                                    const int* const* term_index, const float* bias, const float* w, int rows, int H, float eps, cudaStream_t st) {
+                                    const int* const* term_index, const float* bias, const float* w, int rows, int H, float eps,
+                                    int kind, const float* alpha, const float* shift, cudaStream_t st) {
     if (rows <= 0) return CM_OK;
     if (n_terms < 0 || n_terms > R32_MAX_TERMS) CM_REFUSE("residual_add_norm: %d terms (at most %d)", n_terms, R32_MAX_TERMS);
     if (n_out && !w) CM_REFUSE("residual_add_norm: a norm needs its weight");
+    if (n_out && kind == NORM_DYT && (!alpha || !shift)) CM_REFUSE("residual_add_norm: a dynamic tanh needs its alpha and its shift");
     size_t smem;
     if (row_smem(H, &smem) != CM_OK) return CM_ERR_SHAPE;
     ResidualTerms terms;
@@ -144,10 +166,10 @@ extern "C" int cm_residual_add_norm(int dt, float* h, void* n_out, int n_terms, 
     }
     if (dt == DT_F32) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(residual_add_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cm_launch(residual_add_norm_kernel<float>, rows, R32_THREADS, smem, st, h, (float*)n_out, terms, bias, w, H, eps);
+        cm_launch(residual_add_norm_kernel<float>, rows, R32_THREADS, smem, st, h, (float*)n_out, terms, bias, w, H, eps, kind, alpha, shift);
     } else if (dt == DT_BF16) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(residual_add_norm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cm_launch(residual_add_norm_kernel<bf16>, rows, R32_THREADS, smem, st, h, (bf16*)n_out, terms, bias, w, H, eps);
+        cm_launch(residual_add_norm_kernel<bf16>, rows, R32_THREADS, smem, st, h, (bf16*)n_out, terms, bias, w, H, eps, kind, alpha, shift);
     } else
         return CM_ERR_DTYPE;
     CM_CHECK_LAUNCH();

@@ -402,6 +402,28 @@ extern "C" int cm_swiglu(int dt, void* a, const void* gu, int rows, int F, cudaS
     return CM_OK;
 }
 
+// ------------------------------------------------------------ squared ReLU
+// x <- T(max(x, 0)^2) in place: the activation between the two products of a plain feed-forward.
+template <typename T>
+__global__ void relu2_kernel(T* __restrict__ x, long long total) {
+    pdl_trigger();
+    pdl_wait();
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const float v = fmaxf(to_f32(x[i]), 0.f);
+        x[i] = from_f32<T>(v * v);
+    }
+}
+
+extern "C" int cm_relu2_inplace(int dt, void* x, long long total, cudaStream_t st) {
+    if (total <= 0) return CM_OK;
+    const unsigned blocks = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    if (dt == DT_F32) cm_launch(relu2_kernel<float>, blocks, 256, 0, st, (float*)x, total);
+    else if (dt == DT_BF16) cm_launch(relu2_kernel<bf16>, blocks, 256, 0, st, (bf16*)x, total);
+    else return CM_ERR_DTYPE;
+    CM_CHECK_LAUNCH();
+    return CM_OK;
+}
+
 // ------------------------------------------------------------ logit scale and soft cap
 // x <- cap * tanh((x * scale) / cap), or x * scale when cap is 0: what some architectures do to
 // their logits before sampling.  Float logits, in place.

@@ -5,7 +5,9 @@ configuration, and the order in which they run.
 entry names a block and the state unit (the cache storage) it works on.  A block may appear
 in several entries (it then runs more than once, each run with a state unit of its own), and
 an entry may name a state unit that an earlier entry owns (`owns_state=False`: the layer
-reads another layer's cache and writes none).
+reads another layer's cache and writes none), or list further units in `reads` beside a state of
+its own (a layer that keeps a small state itself and attends over another layer's keys and values:
+the views arrive as `state.borrowed`).
 """
 from __future__ import annotations
 
@@ -19,6 +21,7 @@ class PlanEntry:
     block: int
     state: int
     owns_state: bool = True
+    reads: tuple = ()                # further state units, owned by earlier entries, whose views the block also gets
 
 
 @dataclasses.dataclass
@@ -84,6 +87,7 @@ class ModelDefinition:
                 owned.add(e.state)
                 specs[e.state] = self.blocks[e.block].state_spec()
         for e in self.plan:
-            if not e.owns_state and e.state not in owned:
-                raise ValueError(f"plan reads state unit {e.state}, which no entry owns")
+            for unit in ((e.state,) if not e.owns_state else ()) + tuple(e.reads):
+                if unit not in owned:
+                    raise ValueError(f"plan reads state unit {unit}, which no entry owns")
         return specs

@@ -117,6 +117,8 @@ class DecoderModel:
             state = cache.view(entry.state)
             if state is not None:
                 state.owned, state.unit = entry.owns_state, entry.state
+                if entry.reads:
+                    state.borrowed = [cache.view(u) for u in entry.reads]
             h, n = block.forward(rt, batch, h, n, state, next_norm)
             if n is None and next_norm is not None and i + 1 < len(plan):
                 n = next_norm.apply(rt, h)             # the block left the next block's norm to its caller

@@ -53,8 +53,11 @@ _SIGNATURES = {
     "cm_scatter_i32": [_vp, _vp, _vp, _vp, _i, _vp],
     "cm_zero_slots": [_vp, _i, _ll, _ll, ctypes.POINTER(ctypes.c_int), _i, _vp],
     "cm_copy_pages": [_vp, _vp, _vp, _i, _i, _ll, _ll, _vp],
-    "cm_norm_f32in": [_i, _vp, _vp, _vp, _i, _i, _f, _vp],
-    "cm_residual_add_norm": [_i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp],
+    "cm_norm_f32in": [_i, _vp, _vp, _vp, _i, _i, _f, _i, _vp, _vp, _vp],
+    "cm_residual_add_norm": [_i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp, _vp, _vp],
+    "cm_relu2_inplace": [_i, _vp, _ll, _vp],
+    "cm_tap_rotate_store": [_i, _vp, _vp],
+    "cm_diff_attn": [_i, _vp, _i, _i, _vp],
     "cm_concat_cast": [_i, _vp, _vp, _vp, _ll, _i, _vp],
     "cm_shift_mix": [_i, _vp, _vp, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _i, _ll, _i, _vp],
     "cm_lowrank_decay": [_i, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _vp],
@@ -732,20 +735,35 @@ def zero_slots(store, slots):
 
 
 # ------------------------------------------------------------------ float residual stream
-def norm_f32in(out, x, w, eps):
-    """out = norm(x) * w for float32 rows x; out in the activation dtype."""
+NORM_RMS, NORM_DYT = 0, 1          # csrc/residual32.cu
+
+
+def norm_f32in(out, x, w, eps, dyt=None):
+    """out = norm(x) * w for float32 rows x; out in the activation dtype.  `dyt` = (alpha, shift): a dynamic
+    tanh instead, out = tanh(alpha x) * w + shift (alpha a float32 tensor of one element, shift float32 [H])."""
     _need_cuda(out, x, w)
     rows, H = x.shape
     if x.dtype != torch.float32 or not x.is_contiguous() or not out.is_contiguous():
         raise KernelError("norm_f32in takes contiguous float32 rows")
-    _check(lib().cm_norm_f32in(dtype_code(out.dtype), _ptr(out), _ptr(x), _ptr(w), rows, H, eps, _stream()), "norm_f32in",
+    kind, alpha, shift = (NORM_DYT, dyt[0], dyt[1]) if dyt is not None else (NORM_RMS, None, None)
+    _check(lib().cm_norm_f32in(dtype_code(out.dtype), _ptr(out), _ptr(x), _ptr(w), rows, H, eps, kind, _ptr(alpha),
+                               _ptr(shift), _stream()), "norm_f32in",
            cost=lambda: (f"{rows}x{H}", _nbytes(x, out, w), 4 * rows * H))
 
 
-def residual_add_norm(h, terms, n_out=None, w_next=None, eps=0.0, bias=None):
+def relu2_inplace(x):
+    """x <- max(x, 0)^2, in x's dtype (contiguous)."""
+    if not x.is_contiguous():
+        raise KernelError("relu2_inplace takes a contiguous tensor")
+    _check(lib().cm_relu2_inplace(dtype_code(x.dtype), _ptr(x), x.numel(), _stream()), "relu2_inplace",
+           cost=lambda: (f"{tuple(x.shape)}", 2 * _nbytes(x), 0))
+
+
+def residual_add_norm(h, terms, n_out=None, w_next=None, eps=0.0, bias=None, dyt=None):
     """h (float32, in place) += sum over `terms` of scale * (the sum of a row's pieces) (+ bias, a float32
-    row); n_out = norm(h) * w_next in the activation dtype when given.  A term is (tensor, scale, pieces
-    per row) or (tensor, scale, pieces per row, index): see `Terms`."""
+    row); n_out = norm(h) * w_next in the activation dtype when given (`dyt` = (alpha, shift): a dynamic tanh,
+    as for `norm_f32in`).  A term is (tensor, scale, pieces per row) or (tensor, scale, pieces per row, index):
+    see `Terms`."""
     rows, H = h.shape
     if h.dtype != torch.float32 or not h.is_contiguous() or len(terms) > 4:
         raise KernelError("residual_add_norm: a contiguous float32 stream and at most four terms")
@@ -761,8 +779,9 @@ def residual_add_norm(h, terms, n_out=None, w_next=None, eps=0.0, bias=None):
     per = (ctypes.c_int * 4)(*[int(t[2]) for t in terms], *([0] * (4 - n)))
     f32 = (ctypes.c_int * 4)(*[int(t[0].dtype == torch.float32) for t in terms], *([0] * (4 - n)))
     index = (ctypes.c_void_p * 4)(*[_ptr(t[3]) for t in terms], *([None] * (4 - n)))
+    kind, alpha, shift = (NORM_DYT, dyt[0], dyt[1]) if dyt is not None else (NORM_RMS, None, None)
     _check(lib().cm_residual_add_norm(dtype_code(act), _ptr(h), _ptr(n_out), n, ptrs, scales, per, f32, index, _ptr(bias),
-                                      _ptr(w_next), rows, H, eps, _stream()), "residual_add_norm",
+                                      _ptr(w_next), rows, H, eps, kind, _ptr(alpha), _ptr(shift), _stream()), "residual_add_norm",
            cost=lambda: (f"{rows}x{H}, {n} terms", 2 * _nbytes(h) + _nbytes(n_out) + sum(rows * t[2] * H * t[0].element_size() for t in terms),
                          (n + 5) * rows * H))
 
@@ -825,15 +844,18 @@ class _ScanArgs(ctypes.Structure):
                 ("decay", _vp), ("bonus", _vp), ("norm_w", _vp), ("out", _vp), ("ldo", _ll), ("state", _vp),
                 ("state_stride", _ll), ("state_offset", _ll), ("shift_src", _vp), ("W", _i), ("seq_start", _vp),
                 ("seq_slot", _vp), ("H", _i), ("D", _i), ("DV", _i), ("KS", _i), ("q_scale", _f), ("eps", _f), ("raw", _vp),
-                ("rows", _ll)]
+                ("rows", _ll), ("qkv_act", _i), ("norm_all_heads", _i)]
 
 
 def matrix_scan(mode, out, q, k, v, g, decay, bonus, norm_w, state, state_offset, seq_start, seq_slot, B, H, D, DV,
-                q_scale, eps, shift_src=None):
+                q_scale, eps, shift_src=None, qkv_silu=False, norm_all_heads=False):
     """The recurrence of a mixer with a matrix state per head over the step's rows of B sequences, with the
     heads' unit norm, channel weights and output gate.  mode "decay": o = (S + diag(bonus) k v^T)^T q, then
     S <- diag(decay_t) S + k v^T (decay float32 [rows, H D]; gate silu(g)).  mode "memory": log-domain
     gates with a running maximum and a normaliser (decay float32 [rows, 2 H]: i, then f; gate sigmoid(g)).
+    mode "constant": S <- w S + k v^T, o = S^T q with one decay per head (decay float32 [H]; gate sigmoid(g));
+    `qkv_silu`: q, k and v pass through silu as they are read.  `norm_all_heads`: the unit norm runs over all
+    heads of a row together.
     q, k [rows, H D], v, g, out [rows, H DV]: activation dtype, any row pitch.  state: float32 [slots, n];
     this mixer's part of a row starts at `state_offset`.  `shift_src` [rows, W] (mode "decay"): its last
     row of each sequence is kept at the head of the state row."""
@@ -846,12 +868,83 @@ def matrix_scan(mode, out, q, k, v, g, decay, bonus, norm_w, state, state_offset
                   ldg=g.stride(0), decay=_ptr(decay), bonus=_ptr(bonus), norm_w=_ptr(norm_w), out=_ptr(out),
                   ldo=out.stride(0), state=_ptr(state), state_stride=state.stride(0), state_offset=state_offset,
                   shift_src=_ptr(shift_src), W=0 if shift_src is None else shift_src.shape[1], seq_start=_ptr(seq_start),
-                  seq_slot=_ptr(seq_slot), H=H, D=D, DV=DV, KS=0, q_scale=q_scale, eps=eps)
-    _check(lib().cm_matrix_scan(dtype_code(out.dtype), {"decay": 0, "memory": 1}[mode], ctypes.byref(a), B, _stream()),
+                  seq_slot=_ptr(seq_slot), H=H, D=D, DV=DV, KS=0, q_scale=q_scale, eps=eps, qkv_act=int(qkv_silu),
+                  norm_all_heads=int(norm_all_heads))
+    if mode == "constant" and (decay.dtype != torch.float32 or decay.numel() != H):
+        raise KernelError("matrix_scan: mode 'constant' takes one float32 decay per head")
+    _check(lib().cm_matrix_scan(dtype_code(out.dtype), {"decay": 0, "memory": 1, "constant": 2}[mode], ctypes.byref(a), B, _stream()),
            "matrix_scan_" + mode, 2,
            cost=lambda: (f"{B} sequences, {rows} rows, {H} heads of {D}x{DV}",
                          _nbytes(q, k, v, g, out) + (0 if decay is None else rows * decay.shape[1] * 4) + 2 * B * H * D * DV * 4,
                          6 * rows * H * D * DV))
+
+
+# ------------------------------------------------------------------ attention as a difference of two maps
+class _TapRotArgs(ctypes.Structure):
+    """csrc/diffattn.cu: TapRotArgs."""
+    _fields_ = [("proj", _vp), ("ldp", _ll), ("bias", _vp), ("taps", _vp), ("state", _vp), ("state_stride", _ll),
+                ("q_out", _vp), ("ldq", _ll), ("pool", _vp), ("pages", _ll), ("ptab", _vp), ("ptab_stride", _ll),
+                ("rate", _vp), ("mag", _f), ("tok_seq", _vp), ("tok_pos", _vp), ("seq_start", _vp), ("seq_pos0", _vp),
+                ("seq_slot", _vp)] + [(n, _i) for n in ("T", "B", "QC", "KC", "VC", "K", "sub", "rot", "G", "KW", "DV", "HDC",
+                                                        "one_token_each")]
+
+
+def tap_rotate_store(proj, bias, taps, state, q_out, batch, q_channels, sub, rate, mag, kv=None, one_token_each=False):
+    """Short causal taps over the leading channels of the projected rows `proj` (q, then k and v when this layer
+    has them), the partial rotation of q and k, and the cache write.  bias float32 [C] or None; taps float32
+    [C, K]; state float32 [slots, >= (K - 1) C] (the last K - 1 projected rows of every sequence, moved on by
+    this call); q_out [T, q_channels] receives the queries.  `sub`: channels of one rotated vector; rate float32
+    [rot / 2] or None; mag: the factor on sine and cosine.  kv = (pool, pages, ptab, G, key row width, value row
+    width): this layer's pages [2, pages, G, PAGE_TOKENS, HDC]; keys and values follow q in `proj`."""
+    T = proj.shape[0]
+    C, K = taps.shape
+    G = KW = DV = HDC = 0
+    pool = ptab = None
+    pages = 0
+    if kv is not None:
+        pool, pages, ptab, G, KW, DV = kv
+        HDC = pool.shape[-1]
+    if C != q_channels + G * (KW + DV) or proj.shape[1] < C or proj.stride(1) != 1 or q_out.dtype != proj.dtype:
+        raise KernelError("tap_rotate_store: the projected rows do not hold the channels that the taps name")
+    if not (taps.is_contiguous() and taps.dtype == state.dtype == torch.float32 and state.stride(-1) == 1):
+        raise KernelError("tap_rotate_store: float32 taps and state")
+    a = _TapRotArgs(proj=_ptr(proj), ldp=proj.stride(0), bias=_ptr(bias), taps=_ptr(taps), state=_ptr(state),
+                    state_stride=state.stride(0), q_out=_ptr(q_out), ldq=q_out.stride(0), pool=_ptr(pool), pages=pages,
+                    ptab=_ptr(ptab), ptab_stride=0 if ptab is None else ptab.stride(0), rate=_ptr(rate), mag=mag,
+                    tok_seq=_ptr(batch.tok_seq), tok_pos=_ptr(batch.tok_pos), seq_start=_ptr(batch.seq_start),
+                    seq_pos0=_ptr(batch.seq_pos0), seq_slot=_ptr(batch.seq_slot), T=T, B=batch.B, QC=q_channels,
+                    KC=G * KW, VC=G * DV, K=K, sub=sub, rot=0 if rate is None else 2 * rate.numel(), G=G, KW=KW, DV=DV,
+                    HDC=HDC, one_token_each=int(one_token_each))
+    _check(lib().cm_tap_rotate_store(dtype_code(proj.dtype), ctypes.byref(a), _stream()), "tap_rotate_store",
+           1 if one_token_each or K < 2 else 2,
+           cost=lambda: (f"{T}x{C}, {K} taps", 2 * T * C * proj.element_size(), 2 * K * T * C))
+
+
+class _DiffAttnArgs(ctypes.Structure):
+    """csrc/diffattn.cu: DiffAttnArgs."""
+    _fields_ = [("ctx", _vp), ("ldc", _ll), ("q", _vp), ("ldq", _ll), ("gate", _vp), ("ldg", _ll), ("pool", _vp),
+                ("pages", _ll), ("ptab", _vp), ("ptab_stride", _ll), ("tok_seq", _vp), ("tok_pos", _vp), ("seq_start", _vp),
+                ("seq_pos0", _vp), ("seq_slot", _vp)] + [(n, _i) for n in ("T", "B", "H", "G", "D", "DV", "HDC", "window", "keep")] \
+               + [(n, _f) for n in ("scale", "lam", "out_scale", "eps")]
+
+
+def diff_attn(ctx, q, gate, pool, pages, ptab, batch, H, G, D, DV, window, keep, scale, lam, out_scale, eps, rows_form):
+    """Attention whose output is the difference of two softmax maps over the same values, read from the paged
+    cache: q [T, H * 2 * D] (per head map 1, then map 2), ctx [T, H * DV]; a key at j is visible from i when
+    j <= i and (i - j < window or j < keep) (window <= 0: all j <= i); o = a1 - lam * a2, brought to unit root mean
+    square per head, times out_scale and sigmoid(gate[t, head]) (gate may be None).  `rows_form`: a block per row
+    and head (steps of one token a sequence); else tiles of queries, launched for batch.max_len rows a sequence."""
+    T = q.shape[0]
+    if q.stride(1) != 1 or ctx.stride(1) != 1 or q.dtype != ctx.dtype or pool.dtype != q.dtype:
+        raise KernelError("diff_attn: row-major operands and a cache of one dtype")
+    a = _DiffAttnArgs(ctx=_ptr(ctx), ldc=ctx.stride(0), q=_ptr(q), ldq=q.stride(0), gate=_ptr(gate),
+                      ldg=0 if gate is None else gate.stride(0), pool=_ptr(pool), pages=pages, ptab=_ptr(ptab),
+                      ptab_stride=ptab.stride(0), tok_seq=_ptr(batch.tok_seq), tok_pos=_ptr(batch.tok_pos),
+                      seq_start=_ptr(batch.seq_start), seq_pos0=_ptr(batch.seq_pos0), seq_slot=_ptr(batch.seq_slot), T=T,
+                      B=batch.B, H=H, G=G, D=D, DV=DV, HDC=pool.shape[-1], window=window, keep=keep, scale=scale, lam=lam,
+                      out_scale=out_scale, eps=eps)
+    _check(lib().cm_diff_attn(dtype_code(q.dtype), ctypes.byref(a), int(rows_form), batch.max_len, _stream()), "diff_attn",
+           cost=lambda: (f"{batch.B} sequences, {T} rows, {H}/{G} heads of 2x{D}, {DV}, window {window}+{keep}", 0, 0))
 
 
 # ------------------------------------------------------------------ routed feed-forward

@@ -34,4 +34,30 @@ class SwiGLU(FeedForward):
         return self.down.apply(rt, a, out_dtype=self.out_dtype, partial_ok=batch.partial_sums_ok and self.out_dtype is None)
 
 
+class ReluSquared(FeedForward):
+    """Plain two-matrix feed-forward with a squared ReLU between: W_down max(W_up x, 0)^2."""
+    prompt_capturable = True
+    supports_append = True
+
+    def __init__(self, prefix, hidden, intermediate, names=None, out_dtype=None):
+        import torch
+
+        self.out_dtype = {None: None, "float32": torch.float32}[out_dtype]
+        names = names or {}
+        self.hidden, self.intermediate = hidden, intermediate
+        self.up = Linear(prefix + names.get("up", "up"), intermediate, hidden)
+        self.down = Linear(prefix + names.get("down", "down"), hidden, intermediate)
+
+    def children(self):
+        return [self.up, self.down]
+
+    def forward(self, rt, batch, x):
+        from .. import kernels
+
+        a = self.up.apply(rt, x)
+        kernels.relu2_inplace(a)
+        return self.down.apply(rt, a, out_dtype=self.out_dtype, partial_ok=batch.partial_sums_ok and self.out_dtype is None)
+
+
 register_part("feed_forward", "swiglu", SwiGLU)
+register_part("feed_forward", "relu_squared", ReluSquared)

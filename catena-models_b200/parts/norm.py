@@ -46,4 +46,36 @@ class RMSNorm(Norm):
         return y
 
 
+class DynamicTanh(Norm):
+    """y = tanh(alpha x) * w + b in place of a norm: no mean, no variance, nothing that looks along the row.
+    `alpha` is a learned scalar stored as `<name>.alpha`, the shift as `<name>.b`.  Takes float32 rows (a
+    float32 residual stream) and writes activations; the residual kernel of such a stream applies it in the
+    same launch (`fused_kind`)."""
+    prompt_capturable = True
+    supports_append = True
+    fused_kind = "dyt"
+
+    def __init__(self, name, width):
+        self.name, self.width, self.eps = name, width, 0.0
+        self.weight = self.alpha = self.shift = None
+
+    def tensor_specs(self):
+        return [TensorSpec(self.name, (self.width,), "norm"), TensorSpec(self.name + ".alpha", (), "vector"),
+                TensorSpec(self.name + ".b", (self.width,), "vector")]
+
+    def bind(self, tensors, rt):
+        f32 = lambda n: tensors[n].to(torch.float32).contiguous()
+        self.weight, self.shift = f32(self.name), f32(self.name + ".b")
+        self.alpha = f32(self.name + ".alpha").reshape(1)
+        self._bound = [self.weight, self.shift, self.alpha]
+
+    def apply(self, rt, x):
+        if x.dtype != torch.float32:
+            raise NotImplementedError("the dynamic tanh reads float32 rows (ModelDefinition.residual_float32)")
+        y = torch.empty(x.shape, dtype=rt.dtype, device=x.device)
+        kernels.norm_f32in(y, x.contiguous(), self.weight, 0.0, dyt=(self.alpha, self.shift))
+        return y
+
+
 register_part("norm", "rms", RMSNorm)
+register_part("norm", "dynamic_tanh", DynamicTanh)

@@ -7,6 +7,9 @@ its own state (the layer's state spec is the pair of theirs).
 feed_forward(n)); the feed-forward may be absent.  The sum of all terms, the float32 residual sum and the
 norm of whatever runs next are one kernel (`residual_add_norm`), as the sandwich block's `add_norm` is.
 
+`PreNormBlock`: the sequential arrangement on the same stream: a norm and a mixer, then a norm and a
+feed-forward, each sum with a constant factor.
+
 `LoopEntry`: the step between two passes of a looped stack: h <- W [h; h0] + step, h0 being the embedding
 rows of the batch (the definition keeps them: `keep_embedding`) and `step` a learned row of the pass.  It
 has no norm of its own and no state; the product's float32 result becomes the new residual stream, and the
@@ -77,11 +80,50 @@ class ParallelBlock(Block):
 
 
 def _sum_and_norm(rt, h, terms, bias, next_norm):
-    """h += terms (+ bias); the next norm in the same kernel when it is an RMS norm."""
-    fuse = next_norm is not None and getattr(next_norm, "fused_kind", None) == "rms"
+    """h += terms (+ bias); the next norm in the same kernel when it is an RMS norm or a dynamic tanh."""
+    kind = getattr(next_norm, "fused_kind", None) if next_norm is not None else None
+    fuse = kind in ("rms", "dyt")
     n_out = torch.empty(h.shape, dtype=rt.dtype, device=h.device) if fuse else None
-    kernels.residual_add_norm(h, terms, n_out, next_norm.weight if fuse else None, next_norm.eps if fuse else 0.0, bias)
+    kernels.residual_add_norm(h, terms, n_out, next_norm.weight if fuse else None, next_norm.eps if fuse else 0.0, bias,
+                              dyt=(next_norm.alpha, next_norm.shift) if kind == "dyt" else None)
     return h, n_out
+
+
+class PreNormBlock(Block):
+    """Two sublayers one after the other on a float32 stream, each behind a norm of its own and each added with
+    the same constant factor: h <- h + c * mixer(norm1(h)), then h <- h + c * feed_forward(norm2(h)); the
+    feed-forward (and its norm) may be absent.  Each sum forms the norm of whatever reads the stream next."""
+    prompt_capturable = True
+    supports_append = True
+
+    def __init__(self, mixer, feed_forward, input_norm, ffn_norm, residual_scale=1.0):
+        if (feed_forward is None) != (ffn_norm is None):
+            raise ValueError("a feed-forward and its norm come together")
+        self.mixer, self.feed_forward, self.input_norm, self.ffn_norm = mixer, feed_forward, input_norm, ffn_norm
+        self.residual_scale = float(residual_scale)
+
+    def children(self):
+        return [p for p in (self.input_norm, self.mixer, self.ffn_norm, self.feed_forward) if p is not None]
+
+    def state_spec(self):
+        return self.mixer.state_spec()
+
+    def _scaled(self, y):
+        return kernels.Terms([(e[0], e[1] * self.residual_scale, *e[2:]) for e in _terms(y)])
+
+    def forward(self, rt, batch, h, n, state, next_norm):
+        if h.dtype != torch.float32:
+            raise ValueError("PreNormBlock works on a float32 residual stream (ModelDefinition.residual_float32)")
+        batch.partial_sums_ok = False
+        if n is None:
+            n = self.input_norm.apply(rt, h)
+        y = self._scaled(self.mixer.forward(rt, batch, n, state))
+        if self.feed_forward is None:
+            return _sum_and_norm(rt, h, y, None, next_norm)
+        h, n2 = _sum_and_norm(rt, h, y, None, self.ffn_norm)
+        if n2 is None:
+            n2 = self.ffn_norm.apply(rt, h)
+        return _sum_and_norm(rt, h, self._scaled(self.feed_forward.forward(rt, batch, n2)), None, next_norm)
 
 
 class LoopEntry(Block):
@@ -112,4 +154,5 @@ class LoopEntry(Block):
 
 register_part("mixer", "side_by_side", SideBySide)
 register_part("block", "parallel", ParallelBlock)
+register_part("block", "prenorm", PreNormBlock)
 register_part("block", "loop_entry", LoopEntry)

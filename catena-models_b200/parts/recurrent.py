@@ -147,5 +147,50 @@ class MatrixMemory(Mixer):
         return self.out.apply(rt, o, out_dtype=self.out_dtype)
 
 
+class ConstantDecayMemory(Mixer):
+    """Linear attention with one constant decay per head (lightning attention): q, k (heads x dim) and v
+    (heads x value_dim) pass through silu; per head S_t = w S_(t-1) + k_t v_t^T and o_t = S_t^T q_t, with no
+    other scale; all heads of a token together are brought to unit root mean square, then times a channel
+    weight and sigmoid(W_g h), then the output projection.  State per sequence: S, float32."""
+    prompt_capturable = True
+    supports_append = True
+
+    def __init__(self, prefix, hidden, heads, dim, value_dim, decay, eps, out_dtype=None):
+        if len(decay) != heads:
+            raise ValueError(f"{len(decay)} decays for {heads} heads")
+        self.hidden, self.heads, self.dim, self.value_dim = hidden, heads, dim, value_dim
+        self.eps, self.prefix, self.decay_values = float(eps), prefix, [float(w) for w in decay]
+        self.k_size, self.v_size = heads * dim, heads * value_dim
+        self.qkvg = Linear([prefix + "q", prefix + "k", prefix + "v", prefix + "g"],
+                           [self.k_size, self.k_size, self.v_size, self.v_size], hidden)
+        self.out = Linear(prefix + "o", hidden, self.v_size)
+        self.out_dtype = {None: None, "float32": torch.float32}[out_dtype]
+
+    def children(self):
+        return [self.qkvg, self.out]
+
+    def tensor_specs(self):
+        return [TensorSpec(self.prefix + "norm", (self.v_size,), "vector")]
+
+    def bind(self, tensors, rt):
+        self.norm_w = tensors[self.prefix + "norm"].to(torch.float32).contiguous()
+        self.decay = torch.tensor(self.decay_values, dtype=torch.float32, device=rt.device)
+        self._bound = [self.norm_w, self.decay]
+
+    def state_spec(self):
+        return FixedStateSpec((self.heads * self.dim * self.value_dim,), "float32")
+
+    def forward(self, rt, batch, x, state):
+        T, KS, VS = batch.T, self.k_size, self.v_size
+        proj = self.qkvg.apply(rt, x)
+        o = torch.empty((T, VS), dtype=x.dtype, device=x.device)
+        kernels.matrix_scan("constant", o, proj[:, :KS], proj[:, KS:2 * KS], proj[:, 2 * KS:2 * KS + VS],
+                            proj[:, 2 * KS + VS:], self.decay, None, self.norm_w, state.tensor, 0, batch.seq_start,
+                            batch.seq_slot, batch.B, self.heads, self.dim, self.value_dim, 1.0, self.eps,
+                            qkv_silu=True, norm_all_heads=True)
+        return self.out.apply(rt, o, out_dtype=self.out_dtype)
+
+
 register_part("mixer", "decay_mix", DecayMix)
+register_part("mixer", "constant_decay_memory", ConstantDecayMemory)
 register_part("mixer", "matrix_memory", MatrixMemory)

@@ -41,6 +41,42 @@ class Rotary(Position):
         return self._rate
 
 
+class PartialYarnRotary(Position):
+    """Rotation of the leading `dims` channels of a vector, channel i against channel i + dims/2, with rates
+    rescaled for a longer context than the one trained on (YaRN): with f_i = theta^(-2i/dims), turn(t) =
+    dims ln(original / (2 pi t)) / (2 ln theta), lo = max(floor(turn(fast)), 0), hi = min(ceil(turn(slow)),
+    dims - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i turns at
+    f_i / factor * ramp_i + f_i (1 - ramp_i), and sine and cosine are multiplied by `magnitude` = 0.1 ln(factor)
+    + 1.  Without `factor` the rates are the plain f_i and the magnitude is 1.  The rates are formed in double
+    precision on the host and kept as float32; the kernel forms angle = float(position) * rate."""
+    prompt_capturable = True
+    supports_append = True
+
+    def __init__(self, dims, theta, factor=None, original=None, fast=None, slow=None):
+        import math
+
+        if dims % 2:
+            raise ValueError(f"{dims} turned channels: an even number is needed")
+        self.dims, self.theta = dims, float(theta)
+        half = dims // 2
+        rates = [self.theta ** (-2.0 * i / dims) for i in range(half)]
+        self.magnitude = 1.0
+        if factor is not None:
+            turn = lambda t: dims * math.log(original / (2.0 * math.pi * t)) / (2.0 * math.log(self.theta))
+            lo, hi = max(math.floor(turn(fast)), 0), min(math.ceil(turn(slow)), dims - 1)
+            ramp = [min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0) for i in range(half)]
+            rates = [f / factor * r + f * (1.0 - r) for f, r in zip(rates, ramp)]
+            self.magnitude = 0.1 * math.log(factor) + 1.0
+        self.rates = rates
+        self._rate = None
+
+    def bind(self, tensors, rt):
+        self._rate = torch.tensor(self.rates, dtype=torch.float64).to(torch.float32).to(rt.device).contiguous()
+
+    def rate_table(self):
+        return self._rate
+
+
 class NoPosition(Position):
     """No position encoding: the head vectors are left unrotated."""
     prompt_capturable = True
@@ -50,3 +86,4 @@ class NoPosition(Position):
 
 register_part("position", "rotary", Rotary)
 register_part("position", "none", NoPosition)
+register_part("position", "partial_yarn_rotary", PartialYarnRotary)
