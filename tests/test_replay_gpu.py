@@ -151,6 +151,29 @@ def test_replay_of_a_narasun_model(tmp_path, name, dtype):
     reqs = {k: tiny_narasun.prompt(n, V, seed=ord(k)) for k, n in {"a": 1, "b": 70, "c": 135, "d": 90}.items()}
     exact = {k: plain_narasun.forward(cfg, tensors, t) for k, t in reqs.items()}
     same = {k: plain_narasun.forward(cfg, tensors, t, bf16=True) for k, t in reqs.items()} if dtype == "bfloat16" else exact
+    _replay_whole_tail_and_together(tmp_path, folder, V, reqs, exact, same, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_replay_of_a_fozedra_model(tmp_path, name, dtype):
+    """The third architecture through the same program, on the same schedule."""
+    import plain_fozedra
+    import tiny_fozedra
+
+    folder = tiny_fozedra.make_folder(tmp_path, name, seed=5)
+    cfg, tensors = tiny_fozedra.load_plain(folder)
+    V = cfg["vocab"]
+    reqs = {k: tiny_fozedra.prompt(n, V, seed=ord(k)) for k, n in {"a": 1, "b": 70, "c": 135, "d": 90}.items()}
+    exact = {k: plain_fozedra.forward(cfg, tensors, t) for k, t in reqs.items()}
+    same = ({k: plain_fozedra.forward(cfg, tensors, t, rd=plain_fozedra.to_bf16) for k, t in reqs.items()}
+            if dtype == "bfloat16" else exact)
+    _replay_whole_tail_and_together(tmp_path, folder, V, reqs, exact, same, dtype)
+
+
+def _replay_whole_tail_and_together(tmp_path, folder, V, reqs, exact, same, dtype):
+    """Requests a (1 token), b (70), c (135), d (90): c whole; d with its last 30 tokens one by one; a, b and c started
+    together and decoded together until each has ended."""
     steps, expect = [], {}
 
     def add(entries, positions, end=()):
