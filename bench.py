@@ -540,6 +540,25 @@ def narasun_config(size, vocab=VOCAB):
                 loop=dict(start=2, stop=4, times=2))
 
 
+def fozedra_config(size, vocab=VOCAB):
+    """For `--compare fozedra`: eight layers of the Fozedra decoder at the same width, heads and feed-forward width as the
+    Narasun model above: three lightning layers (the matrix memory's head sizes) and five attention layers that take the
+    difference of two softmax maps (a window of 1,024 tokens with 64 kept first ones, four taps), two of which read
+    another layer's keys and values; one layer without feed-forward."""
+    z = COMPARE_SIZES[size]
+    light = lambda mlp: dict(type="lightning", mlp=mlp, mixer=dict(
+        heads=z["mem_heads"], dim=z["mem_dim"], vdim=z["mem_vdim"],
+        decay=[round(1.0 - 2.0 ** (-2 - 6 * i / max(1, z["mem_heads"] - 1)), 6) for i in range(z["mem_heads"])]))
+    att = lambda mlp, kv_from=None: dict(type="attention", mlp=mlp, mixer=dict(
+        heads=z["heads"] // 2, kv_heads=z["kv_heads"] // 2, dim=z["head"], vdim=2 * z["head"], conv=4, diff=0.3,
+        scale=z["head"] ** -0.5, mask=dict(size=1024, keep_first=64),
+        rot=dict(dims=z["head"] // 2, base=250000.0, scaling=dict(factor=8.0, original=2048, fast=32.0, slow=1.0)),
+        **({} if kv_from is None else dict(kv_from=kv_from))))
+    dense = dict(kind="dense", ff=z["ff"])
+    layers = [light(dense), att(dense), att(dense, 1), light(None), att(dense), att(dense, 4), light(dense), att(dense)]
+    return dict(architecture="Fozedra", vocab=vocab, width=z["width"], norm=dict(eps=1e-6), residual_mult=0.5, layers=layers)
+
+
 def lfm3_like_config(size, vocab=VOCAB):
     z = COMPARE_SIZES[size]
     return dict(architecture="lfm3", vocab_size=vocab, hidden_size=z["width"], intermediate_size=z["ff"], num_hidden_layers=8,
@@ -617,8 +636,9 @@ def _kernel_rows(torch, model, prompt_len, batch, vocab):
     return out
 
 
-def compare_designs(sizes, prompt_len, batch, steps, pk, tables):
-    """Prefill and decode throughput of the Narasun decoder beside an LFM3 decoder of equal size, random weights."""
+def compare_designs(which, sizes, prompt_len, batch, steps, pk, tables):
+    """Prefill and decode throughput of a design beside the closest earlier one at equal size, random weights: the
+    Narasun decoder beside an LFM3 decoder, the Fozedra decoder beside the Narasun decoder."""
     import torch
 
     from catena_models_b200.api import Model
@@ -630,7 +650,9 @@ def compare_designs(sizes, prompt_len, batch, steps, pk, tables):
           "of copy bandwidth | kernels per decode step |")
     print("|---|---|---|---|---|---|---|---|---|---|")
     for size in sizes:
-        for name, cfg in (("Narasun", narasun_config(size, vocab)), ("LFM3", lfm3_like_config(size, vocab))):
+        pairs = {"narasun": (("Narasun", narasun_config), ("LFM3", lfm3_like_config)),
+                 "fozedra": (("Fozedra", fozedra_config), ("Narasun", narasun_config))}[which]
+        for name, cfg in ((n, make(size, vocab)) for n, make in pairs):
             model = Model.random(cfg, seed=0, std=0.02, dtype="bfloat16", max_tokens=batch * (prompt_len + 256) + 4096,
                                  max_seqs=batch + 1)
             p_ms, d_ms, launches = _timed_steps(torch, model, prompt_len, batch, steps, vocab)
@@ -669,9 +691,9 @@ def main():
                     help="time one decode step and one prompt step kernel by kernel and print the table")
     ap.add_argument("--attention-table", action="store_true",
                     help="time the prompt-attention kernels alone at 2,048, 4,096 and 16,384 tokens and print the table")
-    ap.add_argument("--compare", default=None, choices=["narasun"],
-                    help="instead of the JSON line: prompt and decode throughput of that design beside an LFM3 decoder of "
-                         "equal size (random weights), as a table")
+    ap.add_argument("--compare", default=None, choices=["narasun", "fozedra"],
+                    help="instead of the JSON line: prompt and decode throughput of that design beside the closest earlier "
+                         "one at equal size (random weights: Narasun beside LFM3, Fozedra beside Narasun), as a table")
     ap.add_argument("--compare-sizes", default="1024,2048", help="widths of `--compare`")
     ap.add_argument("--compare-kernels", action="store_true", help="with `--compare`: also each model's kernel tables")
     ap.add_argument("--print-config", action="store_true",
@@ -687,7 +709,7 @@ def main():
                           "no Rust toolchain, no network and no GGUF checkpoint here, and pip finds no Python project in it"}))
         return 0
     if args.compare and args.gpus == 1:
-        compare_designs(args.compare_sizes.split(","), args.prompt_len or 2048, args.batch or 8, min(args.steps, 64), peaks(),
+        compare_designs(args.compare, args.compare_sizes.split(","), args.prompt_len or 2048, args.batch or 8, min(args.steps, 64), peaks(),
                         args.compare_kernels)
         return 0
     if args.gpus != 1:

@@ -2,7 +2,7 @@
 // rotation that come between its projections and its scores.
 //
 //   taps      y_t[c] = sum_j w[c][j] * u_(t - K + 1 + j)[c],  u = projection + bias, zeros before position 0;
-//             the last K - 1 values of u of every sequence are its state (float), so a step may begin anywhere
+//             the last K values of u of every sequence are its state (float, a ring), so a step may begin anywhere
 //   rotation  of the leading `rot` channels of every vector of `sub` channels of q and k: channel i against
 //             channel i + rot/2, angle = float(position) * rate[i], sine and cosine times `mag`
 //   cache     a key/value head g holds, per position, a key row [map 1 | map 2] of 2 D channels and a value
@@ -24,7 +24,7 @@ struct TapRotArgs {
     long long ldp;
     const float* bias;           // [C] or null
     const float* taps;           // [C][K]
-    float* state;                // [slots][state_stride]: (K - 1) rows of C channels, oldest first
+    float* state;                // [slots][state_stride]: a ring of K rows of C channels; position s lies in row s % K
     long long state_stride;
     void* q_out;                 // [T][ldq] activations: the queries after taps and rotation
     long long ldq;
@@ -36,29 +36,38 @@ struct TapRotArgs {
     float mag;
     const int *tok_seq, *tok_pos, *seq_start, *seq_pos0, *seq_slot;
     int T, B, QC, KC, VC, K, sub, rot, G, KW, DV, HDC;
-    int one_token_each;          // every sequence brings one token: the state moves on in the same launch
+    int one_token_each;          // every sequence brings one token on top of held ones: the state moves on in the same launch
 };
 
 #define TR_THREADS 128
 #define TR_MAXK CM_MAX_CONV_TAPS
 
 template <typename T>
+__device__ __forceinline__ float tap_input(const TapRotArgs& a, int c, int t, int pos, int p0, int s, const float* st) {
+    // what the filter of channel c reads at position s <= pos of the token in row t
+    if (s >= p0) return to_f32(((const T*)a.proj)[(long long)(t - (pos - s)) * a.ldp + c]) + (a.bias ? a.bias[c] : 0.f);
+    if (s >= 0) return st[(long long)(s % a.K) * (a.QC + a.KC + a.VC) + c];
+    return 0.f;
+}
+
+template <typename T>
 __device__ __forceinline__ float tap_sum(const TapRotArgs& a, int c, int t, int pos, int p0, const float* st) {
-    const int C = a.QC + a.KC + a.VC, K = a.K;
+    const int K = a.K;
     const float* w = a.taps + (long long)c * K;
-    const float bias = a.bias ? a.bias[c] : 0.f;
+    float u[TR_MAXK];
+#pragma unroll
+    for (int j = 0; j < TR_MAXK; ++j)              // every tap's input is asked for before the first is used
+        u[j] = j < K ? tap_input<T>(a, c, t, pos, p0, pos - K + 1 + j, st) : 0.f;
     float y = 0.f;
-    for (int j = 0; j < K; ++j) {
-        const int s = pos - K + 1 + j;                    // the position this tap reads
-        float u = 0.f;
-        if (s >= p0) u = to_f32(((const T*)a.proj)[(long long)(t - (pos - s)) * a.ldp + c]) + bias;
-        else if (s >= 0) u = st[(long long)(s - (p0 - (K - 1))) * C + c];
-        y = fmaf(w[j], u, y);
-    }
+#pragma unroll
+    for (int j = 0; j < TR_MAXK; ++j)
+        if (j < K) y = fmaf(w[j], u[j], y);
     return y;
 }
 
-// One block per token; threads stride the channels.
+// One thread per token (grid x) and channel.  The state of a sequence is a ring of K rows: the projected row of
+// position s lies in row s % K.  A single token reads positions pos - K + 1 .. pos - 1 and then writes row
+// pos % K, which held position pos - K: nobody reads what it writes, so the state moves on in the same launch.
 template <typename T>
 __global__ void __launch_bounds__(TR_THREADS)
 tap_rotate_store_kernel(const TapRotArgs a) {
@@ -67,31 +76,31 @@ tap_rotate_store_kernel(const TapRotArgs a) {
     const int t = blockIdx.x;
     const int b = a.tok_seq[t];
     if (b < 0) return;
+    const int C = a.QC + a.KC + a.VC;
+    const int c = blockIdx.y * TR_THREADS + threadIdx.x;
+    if (c >= C) return;
     const int pos = a.tok_pos[t], p0 = a.seq_pos0[b];
-    const int C = a.QC + a.KC + a.VC, K = a.K;
     float* st = a.state + (long long)a.seq_slot[b] * a.state_stride;
-    int page = 0;
-    const int row = pos % PAGE_TOKENS;
-    if (a.pool) page = a.ptab[(long long)a.seq_slot[b] * a.ptab_stride + pos / PAGE_TOKENS];
     const int half = a.rot >> 1;
-    for (int c = threadIdx.x; c < C; c += TR_THREADS) {
-        float y = tap_sum<T>(a, c, t, pos, p0, st);
-        const int cr = c < a.QC ? c : c - a.QC;           // channel within q, or within k | v
-        if (c < a.QC + a.KC && a.rate) {
-            const int e = cr % a.sub;
-            if (e < a.rot) {
-                const bool low = e < half;
-                const float other = tap_sum<T>(a, low ? c + half : c - half, t, pos, p0, st);
-                float sn, cs;
-                sincosf((float)pos * a.rate[low ? e : e - half], &sn, &cs);
-                sn *= a.mag;
-                cs *= a.mag;
-                y = low ? y * cs - other * sn : y * cs + other * sn;
-            }
+    float y = tap_sum<T>(a, c, t, pos, p0, st);
+    const int cr = c < a.QC ? c : c - a.QC;           // channel within q, or within k | v
+    if (c < a.QC + a.KC && a.rate) {
+        const int e = cr % a.sub;
+        if (e < a.rot) {
+            const bool low = e < half;
+            const float other = tap_sum<T>(a, low ? c + half : c - half, t, pos, p0, st);
+            float sn, cs;
+            sincosf((float)pos * a.rate[low ? e : e - half], &sn, &cs);
+            sn *= a.mag;
+            cs *= a.mag;
+            y = low ? y * cs - other * sn : y * cs + other * sn;
         }
-        if (c < a.QC) {
-            ((T*)a.q_out)[(long long)t * a.ldq + c] = from_f32<T>(y);
-        } else if (cr < a.KC) {
+    }
+    if (c < a.QC) {
+        ((T*)a.q_out)[(long long)t * a.ldq + c] = from_f32<T>(y);
+    } else {
+        const int page = a.ptab[(long long)a.seq_slot[b] * a.ptab_stride + pos / PAGE_TOKENS], row = pos % PAGE_TOKENS;
+        if (cr < a.KC) {
             const int g = cr / a.KW, off = cr - g * a.KW;
             kv_tile((T*)a.pool, 0, a.pages, page, g, a.G, a.HDC)[(long long)row * a.HDC + off] = from_f32<T>(y);
         } else {
@@ -99,17 +108,12 @@ tap_rotate_store_kernel(const TapRotArgs a) {
             kv_tile((T*)a.pool, 1, a.pages, page, g, a.G, a.HDC)[(long long)row * a.HDC + off] = from_f32<T>(y);
         }
     }
-    if (!a.one_token_each || K < 2) return;
-    // a single token: every read of the state above came from this block; each channel's column then moves on by one
-    __syncthreads();
-    for (int c = threadIdx.x; c < C; c += TR_THREADS) {
-        for (int i = 0; i + 1 < K - 1; ++i) st[(long long)i * C + c] = st[(long long)(i + 1) * C + c];
-        st[(long long)(K - 2) * C + c] = to_f32(((const T*)a.proj)[(long long)t * a.ldp + c]) + (a.bias ? a.bias[c] : 0.f);
-    }
+    if (a.one_token_each && a.K > 1) st[(long long)(pos % a.K) * C + c] = tap_input<T>(a, c, t, pos, p0, pos, st);
 }
 
-// The state after a step of several tokens: one thread per (sequence, channel) gathers the K - 1 last values
-// (from the step's rows, or from the old state where the step was shorter), then stores them.
+// The state after a step of several tokens: the projected rows of the sequence's last K - 1 positions that the
+// step brought go to their rows of the ring (older ones lie there already).  A launch of its own, behind the
+// outputs: a long step overwrites rows that its first tokens read.
 template <typename T>
 __global__ void __launch_bounds__(TR_THREADS)
 tap_state_kernel(const TapRotArgs a) {
@@ -124,21 +128,8 @@ tap_state_kernel(const TapRotArgs a) {
     const int p0 = a.seq_pos0[b], end = p0 + n;
     float* st = a.state + (long long)a.seq_slot[b] * a.state_stride;
     const float bias = a.bias ? a.bias[c] : 0.f;
-    float keep[TR_MAXK];
-#pragma unroll
-    for (int i = 0; i < TR_MAXK; ++i) {
-        if (i >= K - 1) break;
-        const int s = end - (K - 1) + i;
-        float u = 0.f;
-        if (s >= p0) u = to_f32(((const T*)a.proj)[(long long)(s0 + s - p0) * a.ldp + c]) + bias;
-        else if (s >= 0) u = st[(long long)(s - (p0 - (K - 1))) * C + c];
-        keep[i] = u;
-    }
-#pragma unroll
-    for (int i = 0; i < TR_MAXK; ++i) {
-        if (i >= K - 1) break;
-        st[(long long)i * C + c] = keep[i];
-    }
+    for (int s = max(p0, end - (K - 1)); s < end; ++s)
+        st[(long long)(s % K) * C + c] = to_f32(((const T*)a.proj)[(long long)(s0 + s - p0) * a.ldp + c]) + bias;
 }
 
 extern "C" int cm_tap_rotate_store(int dt, const TapRotArgs* args, cudaStream_t st) {
@@ -150,14 +141,14 @@ extern "C" int cm_tap_rotate_store(int dt, const TapRotArgs* args, cudaStream_t 
         CM_REFUSE("tap_rotate_store: %d turned channels in vectors of %d", a.rot, a.sub);
     if ((a.KC || a.VC) && (!a.pool || a.KW > a.HDC || a.DV > a.HDC || a.KC != a.G * a.KW || a.VC != a.G * a.DV))
         CM_REFUSE("tap_rotate_store: %d key and %d value channels do not fit %d heads of %d", a.KC, a.VC, a.G, a.HDC);
-    if (a.state_stride < (long long)(a.K - 1) * C) CM_REFUSE("tap_rotate_store: a state row of %lld floats is too short", a.state_stride);
-    dim3 sgrid((C + TR_THREADS - 1) / TR_THREADS, a.B);
+    if (a.K > 1 && a.state_stride < (long long)a.K * C) CM_REFUSE("tap_rotate_store: a state row of %lld floats is too short", a.state_stride);
+    dim3 grid(a.T, (C + TR_THREADS - 1) / TR_THREADS), sgrid((C + TR_THREADS - 1) / TR_THREADS, a.B);
     if (dt == DT_F32) {
-        cm_launch(tap_rotate_store_kernel<float>, a.T, TR_THREADS, 0, st, a);
+        cm_launch(tap_rotate_store_kernel<float>, grid, TR_THREADS, 0, st, a);
         CM_CHECK_LAUNCH();
         if (!a.one_token_each && a.K > 1) cm_launch(tap_state_kernel<float>, sgrid, TR_THREADS, 0, st, a);
     } else if (dt == DT_BF16) {
-        cm_launch(tap_rotate_store_kernel<bf16>, a.T, TR_THREADS, 0, st, a);
+        cm_launch(tap_rotate_store_kernel<bf16>, grid, TR_THREADS, 0, st, a);
         CM_CHECK_LAUNCH();
         if (!a.one_token_each && a.K > 1) cm_launch(tap_state_kernel<bf16>, sgrid, TR_THREADS, 0, st, a);
     } else
@@ -333,14 +324,39 @@ diff_attn_tile_kernel(const DiffAttnArgs a) {
 }
 
 // -------------------------------------------------------------------------------- a row at a time
-// One block = one row (token) and head; the warps take the visible tiles of 32 keys in turns, each with
-// running maxima and sums of its own, which are merged in warp order.  A lane is a key for the scores
-// (its key's row read straight from the cache) and a set of channels for the value sums.
-#define DR_WARPS 8
+// One block = one row (token), one head and one share of the row's visible keys: the tiles of 32 keys that hold
+// kept first tokens or lie in the row's window are dealt out in turns to the warps of `splits` blocks.  Each warp
+// keeps running maxima and sums of its own; a block merges its warps in warp order, and (with more than one
+// share) leaves maxima, sums and value sums in `parts`, which diff_attn_merge_kernel adds in share order.  A lane is
+// a key for the scores (its key's row read from the cache, 16 bytes at a time where the layout allows) and a set
+// of channels for the value sums.
+#define DR_WARPS 4
+
+template <typename T>
+__device__ __forceinline__ void da_key_dots(const T* kr, const float* Qs, int D, bool vec, float& s1, float& s2) {
+    s1 = s2 = 0.f;
+    if (vec) {
+        for (int d = 0; d < D; d += 8) {
+            float k1[8], k2[8];
+            load8f<T>(kr + d, k1);
+            load8f<T>(kr + D + d, k2);
+#pragma unroll
+            for (int x = 0; x < 8; ++x) {
+                s1 = fmaf(Qs[d + x], k1[x], s1);
+                s2 = fmaf(Qs[D + d + x], k2[x], s2);
+            }
+        }
+    } else {
+        for (int d = 0; d < D; ++d) {
+            s1 = fmaf(Qs[d], to_f32(kr[d]), s1);
+            s2 = fmaf(Qs[D + d], to_f32(kr[D + d]), s2);
+        }
+    }
+}
 
 template <typename T, int NJ>
 __global__ void __launch_bounds__(DR_WARPS * 32)
-diff_attn_row_kernel(const DiffAttnArgs a) {
+diff_attn_row_kernel(const DiffAttnArgs a, float* __restrict__ parts, int splits) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float smem[];
@@ -349,7 +365,7 @@ diff_attn_row_kernel(const DiffAttnArgs a) {
     float* Ms = Qs + D2;                         // [DR_WARPS][4]: m1, l1, m2, l2
     float* As = Ms + DR_WARPS * 4;               // [DR_WARPS][2][DV]
     const long long t = blockIdx.y;
-    const int h = blockIdx.x, g = h / (a.H / a.G);
+    const int h = blockIdx.x, g = h / (a.H / a.G), share = blockIdx.z;
     const int b = a.tok_seq[t];
     if (b < 0) return;
     const int qpos = a.tok_pos[t];
@@ -364,19 +380,16 @@ diff_attn_row_kernel(const DiffAttnArgs a) {
     const int kept_tiles = a.window > 0 ? min((min(a.keep, qpos + 1) + 31) / 32, last_tile + 1) : 0;
     const int win_tile = a.window > 0 ? max(kept_tiles, max(0, qpos - a.window + 1) / 32) : 0;
     const int n_tiles = kept_tiles + (last_tile - win_tile + 1);
-    for (int idx = warp; idx < n_tiles; idx += DR_WARPS) {
+    const bool vec = a.D % 8 == 0 && a.HDC % 8 == 0 && ((uintptr_t)a.pool & 15) == 0;
+    for (int idx = share * DR_WARPS + warp; idx < n_tiles; idx += splits * DR_WARPS) {
         const int tile = idx < kept_tiles ? idx : win_tile + idx - kept_tiles;
         const int kpos = tile * 32 + lane;
         const bool vis = da_visible(kpos, qpos, a.window, a.keep);
         const int page = kpos <= qpos ? prow[kpos / PAGE_TOKENS] : 0;
         float s1 = 0.f, s2 = 0.f;
-        if (vis) {
-            const T* kr = kv_tile((const T*)a.pool, 0, a.pages, page, g, a.G, a.HDC) + (long long)(kpos % PAGE_TOKENS) * a.HDC;
-            for (int d = 0; d < a.D; ++d) {
-                s1 = fmaf(Qs[d], to_f32(kr[d]), s1);
-                s2 = fmaf(Qs[a.D + d], to_f32(kr[a.D + d]), s2);
-            }
-        }
+        if (vis)
+            da_key_dots<T>(kv_tile((const T*)a.pool, 0, a.pages, page, g, a.G, a.HDC) + (long long)(kpos % PAGE_TOKENS) * a.HDC,
+                           Qs, a.D, vec, s1, s2);
         s1 = vis ? s1 * a.scale : -INFINITY;
         s2 = vis ? s2 * a.scale : -INFINITY;
         const float x1 = fmaxf(m1, warp_max(s1)), x2 = fmaxf(m2, warp_max(s2));
@@ -393,12 +406,14 @@ diff_attn_row_kernel(const DiffAttnArgs a) {
             acc2[j] *= f2;
         }
         const unsigned seen = __ballot_sync(0xffffffffu, vis);
+        // a tile of 32 keys lies within one page of 64
+        const int tile_page = __shfl_sync(0xffffffffu, page, __ffs(seen) - 1);
+        const T* vt = kv_tile((const T*)a.pool, 1, a.pages, tile_page, g, a.G, a.HDC) + (long long)((tile * 32) % PAGE_TOKENS) * a.HDC;
+#pragma unroll 4
         for (int kk = 0; kk < 32; ++kk) {
             if (!((seen >> kk) & 1u)) continue;  // an unseen key's values may never have been written
             const float q1 = __shfl_sync(0xffffffffu, p1, kk), q2 = __shfl_sync(0xffffffffu, p2, kk);
-            const int kp = tile * 32 + kk;
-            const int pg = __shfl_sync(0xffffffffu, page, kk);
-            const T* vr = kv_tile((const T*)a.pool, 1, a.pages, pg, g, a.G, a.HDC) + (long long)(kp % PAGE_TOKENS) * a.HDC;
+            const T* vr = vt + (long long)kk * a.HDC;
 #pragma unroll
             for (int j = 0; j < NJ; ++j) {
                 const int d = lane + 32 * j;
@@ -446,15 +461,73 @@ diff_attn_row_kernel(const DiffAttnArgs a) {
             }
         }
     }
+    if (splits == 1) {
+        da_finish<T, NJ>(a, t, h, o1, o2, L1, L2);
+        return;
+    }
+    float* part = parts + ((t * a.H + h) * splits + share) * (long long)(4 + 2 * DV);
+    if (lane == 0) {
+        part[0] = M1;
+        part[1] = L1;
+        part[2] = M2;
+        part[3] = L2;
+    }
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+        const int d = lane + 32 * j;
+        if (d < DV) {
+            part[4 + d] = o1[j];
+            part[4 + DV + d] = o2[j];
+        }
+    }
+}
+
+// The shares of a row and head, added in share order; one warp per (row, head).
+template <typename T, int NJ>
+__global__ void __launch_bounds__(32)
+diff_attn_merge_kernel(const DiffAttnArgs a, const float* __restrict__ parts, int splits) {
+    pdl_trigger();
+    pdl_wait();
+    const long long t = blockIdx.y;
+    const int h = blockIdx.x, lane = threadIdx.x, DV = a.DV;
+    if (a.tok_seq[t] < 0) return;
+    const float* part = parts + (t * a.H + h) * splits * (long long)(4 + 2 * DV);
+    float M1 = -INFINITY, M2 = -INFINITY;
+    for (int s = 0; s < splits; ++s) {
+        M1 = fmaxf(M1, part[s * (4 + 2 * DV)]);
+        M2 = fmaxf(M2, part[s * (4 + 2 * DV) + 2]);
+    }
+    float L1 = 0.f, L2 = 0.f, o1[NJ], o2[NJ];
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) o1[j] = o2[j] = 0.f;
+    for (int s = 0; s < splits; ++s) {
+        const float* ps = part + s * (long long)(4 + 2 * DV);
+        if (ps[0] == -INFINITY) continue;        // a share without a visible tile
+        const float f1 = expf(ps[0] - M1), f2 = expf(ps[2] - M2);
+        L1 = fmaf(ps[1], f1, L1);
+        L2 = fmaf(ps[3], f2, L2);
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) {
+            const int d = lane + 32 * j;
+            if (d < DV) {
+                o1[j] = fmaf(ps[4 + d], f1, o1[j]);
+                o2[j] = fmaf(ps[4 + DV + d], f2, o2[j]);
+            }
+        }
+    }
     da_finish<T, NJ>(a, t, h, o1, o2, L1, L2);
 }
 
 template <typename T, int NJ>
-static int da_launch(const DiffAttnArgs& a, int rows_form, int max_len, cudaStream_t st) {
+static int da_launch(const DiffAttnArgs& a, int rows_form, int max_len, float* parts, int splits, cudaStream_t st) {
     if (rows_form) {
         const size_t smem = ((size_t)2 * a.D + DR_WARPS * 4 + (size_t)DR_WARPS * 2 * a.DV) * sizeof(float);
         if (smem > 48 * 1024) cudaFuncSetAttribute(diff_attn_row_kernel<T, NJ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cm_launch(diff_attn_row_kernel<T, NJ>, dim3(a.H, a.T), DR_WARPS * 32, smem, st, a);
+        cm_launch(diff_attn_row_kernel<T, NJ>, dim3(a.H, a.T, splits), DR_WARPS * 32, smem, st, a, parts, splits);
+        if (splits > 1) {
+            CM_CHECK_LAUNCH();
+            cm_launch(diff_attn_merge_kernel<T, NJ>, dim3(a.H, a.T), 32, 0, st, a, (const float*)parts, splits);
+        }
     } else {
         const size_t smem = ((size_t)(DA_BQ + DA_BK) * (2 * a.D + 1) + (size_t)DA_BK * a.DV + 2 * DA_BQ * (DA_BK + 1)) * sizeof(float);
         if (smem > 200 * 1024) CM_REFUSE("diff_attn: heads of 2 x %d and %d channels do not fit shared memory", a.D, a.DV);
@@ -465,24 +538,27 @@ static int da_launch(const DiffAttnArgs& a, int rows_form, int max_len, cudaStre
     return CM_OK;
 }
 
-// rows_form: one block per row and head (steps of one or few tokens a sequence); else tiles of 32 queries,
-// launched for sequences of up to max_len new tokens.
-extern "C" int cm_diff_attn(int dt, const DiffAttnArgs* args, int rows_form, int max_len, cudaStream_t st) {
+// rows_form: one block per row, head and share of the keys (steps of one or few tokens a sequence), `splits` shares
+// with `parts` [T][H][splits][4 + 2 DV] floats between the two launches (splits 1: one launch, no parts); else tiles
+// of 32 queries, launched for sequences of up to max_len new tokens.
+extern "C" int cm_diff_attn(int dt, const DiffAttnArgs* args, int rows_form, int max_len, float* parts, int splits,
+                            cudaStream_t st) {
     const DiffAttnArgs a = *args;
     if (a.T <= 0 || a.B <= 0) return CM_OK;
     if (a.D <= 0 || a.DV <= 0 || a.DV > CM_MAX_HEAD_DIM || 2 * a.D > a.HDC || a.DV > a.HDC)
         CM_REFUSE("diff_attn: heads of 2 x %d key and %d value channels in entries of %d (values up to %d)", a.D, a.DV, a.HDC, CM_MAX_HEAD_DIM);
     if (a.G <= 0 || a.H % a.G) CM_REFUSE("diff_attn: %d query heads over %d key heads", a.H, a.G);
     if (!rows_form && max_len <= 0) return CM_OK;
+    if (splits < 1 || (splits > 1 && !parts)) CM_REFUSE("diff_attn: %d shares need their scratch", splits);
     const int nj = (a.DV + 31) / 32;
-#define DA_DISPATCH(TT)                                                     \
-    do {                                                                    \
-        if (nj <= 1) return da_launch<TT, 1>(a, rows_form, max_len, st);    \
-        if (nj == 2) return da_launch<TT, 2>(a, rows_form, max_len, st);    \
-        if (nj == 3) return da_launch<TT, 3>(a, rows_form, max_len, st);    \
-        if (nj == 4) return da_launch<TT, 4>(a, rows_form, max_len, st);    \
-        if (nj <= 6) return da_launch<TT, 6>(a, rows_form, max_len, st);    \
-        return da_launch<TT, 8>(a, rows_form, max_len, st);                 \
+#define DA_DISPATCH(TT)                                                                    \
+    do {                                                                                   \
+        if (nj <= 1) return da_launch<TT, 1>(a, rows_form, max_len, parts, splits, st);    \
+        if (nj == 2) return da_launch<TT, 2>(a, rows_form, max_len, parts, splits, st);    \
+        if (nj == 3) return da_launch<TT, 3>(a, rows_form, max_len, parts, splits, st);    \
+        if (nj == 4) return da_launch<TT, 4>(a, rows_form, max_len, parts, splits, st);    \
+        if (nj <= 6) return da_launch<TT, 6>(a, rows_form, max_len, parts, splits, st);    \
+        return da_launch<TT, 8>(a, rows_form, max_len, parts, splits, st);                 \
     } while (0)
     if (dt == DT_F32) DA_DISPATCH(float);
     if (dt == DT_BF16) DA_DISPATCH(bf16);

@@ -57,7 +57,7 @@ _SIGNATURES = {
     "cm_residual_add_norm": [_i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp, _vp, _vp],
     "cm_relu2_inplace": [_i, _vp, _ll, _vp],
     "cm_tap_rotate_store": [_i, _vp, _vp],
-    "cm_diff_attn": [_i, _vp, _i, _i, _vp],
+    "cm_diff_attn": [_i, _vp, _i, _i, _vp, _i, _vp],
     "cm_concat_cast": [_i, _vp, _vp, _vp, _ll, _i, _vp],
     "cm_shift_mix": [_i, _vp, _vp, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _i, _ll, _i, _vp],
     "cm_lowrank_decay": [_i, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _vp],
@@ -875,7 +875,7 @@ def matrix_scan(mode, out, q, k, v, g, decay, bonus, norm_w, state, state_offset
     _check(lib().cm_matrix_scan(dtype_code(out.dtype), {"decay": 0, "memory": 1, "constant": 2}[mode], ctypes.byref(a), B, _stream()),
            "matrix_scan_" + mode, 2,
            cost=lambda: (f"{B} sequences, {rows} rows, {H} heads of {D}x{DV}",
-                         _nbytes(q, k, v, g, out) + (0 if decay is None else rows * decay.shape[1] * 4) + 2 * B * H * D * DV * 4,
+                         _nbytes(q, k, v, g, out) + (0 if decay is None or decay.dim() < 2 else rows * decay.shape[1] * 4) + 2 * B * H * D * DV * 4,
                          6 * rows * H * D * DV))
 
 
@@ -892,7 +892,7 @@ class _TapRotArgs(ctypes.Structure):
 def tap_rotate_store(proj, bias, taps, state, q_out, batch, q_channels, sub, rate, mag, kv=None, one_token_each=False):
     """Short causal taps over the leading channels of the projected rows `proj` (q, then k and v when this layer
     has them), the partial rotation of q and k, and the cache write.  bias float32 [C] or None; taps float32
-    [C, K]; state float32 [slots, >= (K - 1) C] (the last K - 1 projected rows of every sequence, moved on by
+    [C, K]; state float32 [slots, >= K C] (a ring of the last K projected rows of every sequence, moved on by
     this call); q_out [T, q_channels] receives the queries.  `sub`: channels of one rotated vector; rate float32
     [rot / 2] or None; mag: the factor on sine and cosine.  kv = (pool, pages, ptab, G, key row width, value row
     width): this layer's pages [2, pages, G, PAGE_TOKENS, HDC]; keys and values follow q in `proj`."""
@@ -928,12 +928,28 @@ class _DiffAttnArgs(ctypes.Structure):
                + [(n, _f) for n in ("scale", "lam", "out_scale", "eps")]
 
 
-def diff_attn(ctx, q, gate, pool, pages, ptab, batch, H, G, D, DV, window, keep, scale, lam, out_scale, eps, rows_form):
+DIFF_ATTN_ROW_WARPS, DIFF_ATTN_MAX_SPLITS = 4, 16      # csrc/diffattn.cu: warps of a block of the rows form; most shares
+
+
+def diff_attn_splits(rows, H, keys, sm_count=148):
+    """Into how many shares the rows form cuts a row's visible keys (at most `keys` of them): enough blocks for two per
+    SM, while every warp still has a tile of 32 keys."""
+    tiles = -(-max(1, keys) // 32)
+    want = -(-2 * sm_count // max(1, rows * H))
+    return max(1, min(DIFF_ATTN_MAX_SPLITS, want, -(-tiles // DIFF_ATTN_ROW_WARPS)))
+
+
+def diff_attn(ctx, q, gate, pool, pages, ptab, batch, H, G, D, DV, window, keep, scale, lam, out_scale, eps, rows_form,
+              parts=None, splits=1):
     """Attention whose output is the difference of two softmax maps over the same values, read from the paged
     cache: q [T, H * 2 * D] (per head map 1, then map 2), ctx [T, H * DV]; a key at j is visible from i when
     j <= i and (i - j < window or j < keep) (window <= 0: all j <= i); o = a1 - lam * a2, brought to unit root mean
     square per head, times out_scale and sigmoid(gate[t, head]) (gate may be None).  `rows_form`: a block per row
-    and head (steps of one token a sequence); else tiles of queries, launched for batch.max_len rows a sequence."""
+    and head (steps of one token a sequence), whose visible keys may be cut into `splits` shares with float32 scratch
+    `parts` of at least T * H * splits * (4 + 2 DV) elements between two launches; else tiles of queries, launched for
+    batch.max_len rows a sequence."""
+    if splits > 1 and (parts is None or parts.dtype != torch.float32 or parts.numel() < T_need(q, H, splits, DV)):
+        raise KernelError("diff_attn: the shares' scratch is missing or too small")
     T = q.shape[0]
     if q.stride(1) != 1 or ctx.stride(1) != 1 or q.dtype != ctx.dtype or pool.dtype != q.dtype:
         raise KernelError("diff_attn: row-major operands and a cache of one dtype")
@@ -943,8 +959,24 @@ def diff_attn(ctx, q, gate, pool, pages, ptab, batch, H, G, D, DV, window, keep,
                       seq_start=_ptr(batch.seq_start), seq_pos0=_ptr(batch.seq_pos0), seq_slot=_ptr(batch.seq_slot), T=T,
                       B=batch.B, H=H, G=G, D=D, DV=DV, HDC=pool.shape[-1], window=window, keep=keep, scale=scale, lam=lam,
                       out_scale=out_scale, eps=eps)
-    _check(lib().cm_diff_attn(dtype_code(q.dtype), ctypes.byref(a), int(rows_form), batch.max_len, _stream()), "diff_attn",
-           cost=lambda: (f"{batch.B} sequences, {T} rows, {H}/{G} heads of 2x{D}, {DV}, window {window}+{keep}", 0, 0))
+    _check(lib().cm_diff_attn(dtype_code(q.dtype), ctypes.byref(a), int(rows_form), batch.max_len, _ptr(parts), splits,
+                              _stream()), "diff_attn", 2 if rows_form and splits > 1 else 1,
+           cost=lambda: _diff_attn_cost(batch, T, H, G, D, DV, window, keep, q.element_size(), rows_form))
+
+
+def T_need(q, H, splits, DV):
+    return q.shape[0] * H * splits * (4 + 2 * DV)
+
+
+def _diff_attn_cost(batch, T, H, G, D, DV, window, keep, esz, rows_form):
+    """(shape text, bytes, floating-point operations) by definition: the keys a row sees are those of its window and the
+    kept ones, half of its sequence for a prompt from position 0; every key and value row is read once per sequence."""
+    reach = batch.max_end if rows_form else max(1, batch.max_end // 2)
+    seen = min(reach, window + keep) if window > 0 else reach
+    held = min(batch.max_end, window + keep + (0 if rows_form else batch.max_len)) if window > 0 else batch.max_end
+    nbytes = batch.B * held * G * (2 * D + DV) * esz + T * H * (2 * D + DV) * esz
+    return (f"{batch.B} sequences, {T} rows, {H}/{G} heads of 2x{D}, {DV}, window {window}+{keep}", nbytes,
+            2 * 2 * T * seen * H * (D + DV))
 
 
 # ------------------------------------------------------------------ routed feed-forward

@@ -19,7 +19,7 @@ A layer with `shares_kv` has no key and value tensors: it attends over the cache
 unit the plan lends it (`PlanEntry.reads`), with queries, taps, mask and lambda of its own.
 
 State: the pages of keys and values (every position is kept, since kept first tokens rule out a ring), and
-the last taps - 1 projected rows (float32).  Every kind of step runs the same two kernels, which read all keys
+the last `taps` projected rows (float32; the row of position s lies in row s % taps).  Every kind of step runs the same two kernels, which read all keys
 from the cache, so whole prompts, portions and single tokens agree.
 """
 from __future__ import annotations
@@ -77,7 +77,7 @@ class DiffAttention(Mixer):
         self._bound = [self.bias, self.tap_w]
 
     def state_spec(self):
-        own = FixedStateSpec((max(1, (self.taps - 1) * self.channels),), "float32")
+        own = FixedStateSpec((max(1, self.taps * self.channels if self.taps > 1 else 1),), "float32")   # a ring of `taps` rows
         if self.shares_kv:
             return own
         return CompositeStateSpec((KVStateSpec(self.kv_heads, self.cache_head, 0), own))
@@ -98,8 +98,17 @@ class DiffAttention(Mixer):
                                  kv=None if self.shares_kv else (kv.pool, kv.pages, kv.ptab, G, 2 * D, DV),
                                  one_token_each=one_each)
         ctx = torch.empty((batch.T, H * DV), dtype=x.dtype, device=x.device)
+        parts, splits = None, 1
+        if one_each:
+            # sized by the longest sequence that the step's class of lengths allows, so that a recording serves the class
+            reach = kv.spec.entries(kv.spec.length_class(batch.max_end))
+            keys = min(reach, self.window + self.keep_first) if self.window > 0 else reach
+            splits = kernels.diff_attn_splits(batch.T, H, keys)
+            if splits > 1:
+                parts = rt.scratch("diff_attn_parts", batch.T * H * splits * (4 + 2 * DV))
         kernels.diff_attn(ctx, q, proj[:, self.channels:], kv.pool, kv.pages, kv.ptab, batch, H, G, D, DV, self.window,
-                          self.keep_first, self.scale, self.lam, 1.0 - self.diff, self.eps, rows_form=one_each)
+                          self.keep_first, self.scale, self.lam, 1.0 - self.diff, self.eps, rows_form=one_each,
+                          parts=parts, splits=splits)
         return self.out.apply(rt, ctx, out_dtype=self.out_dtype)
 
 

@@ -27,8 +27,8 @@ def test_plan_lends_the_owner_state_to_a_reader():
     specs = d.state_specs()
     assert isinstance(specs[0], CompositeStateSpec) and isinstance(specs[0].parts[0], KVStateSpec)
     assert specs[0].parts[0] == KVStateSpec(2, 32, 0)                  # a key row of 2 x 16, a value row of 8: entries of 32
-    assert specs[0].parts[1] == FixedStateSpec((3 * (4 * 32 + 2 * 32 + 2 * 8),), "float32")
-    assert specs[1] == FixedStateSpec((3 * 4 * 32,), "float32")         # a reader filters its queries only
+    assert specs[0].parts[1] == FixedStateSpec((4 * (4 * 32 + 2 * 32 + 2 * 8),), "float32")   # a ring of four rows
+    assert specs[1] == FixedStateSpec((4 * 4 * 32,), "float32")         # a reader filters its queries only
     names = {s.name for s in d.tensor_specs()}
     assert "l1.mix.q.conv" in names and "l1.mix.k" not in names and "l1.mix.v.b" not in names
     assert "l0.mix.k.conv" in names and "l2.mix.norm" in names and "final.norm.alpha" in names

@@ -152,7 +152,7 @@ def _run_taps(c, cuts, slots, dtype=torch.float32, pool=None, state=None):
         ids = torch.randperm(8 * pages_per, generator=torch.Generator().manual_seed(9)).to(torch.int32).view(8, pages_per)
         ptab.copy_(ids.to(DEV))
     if state is None:
-        state = torch.full((8, max(1, (c["K"] - 1) * c["C"])), float("nan"), device=DEV)
+        state = torch.full((8, max(1, c["K"] * c["C"])), float("nan"), device=DEV)
     kernels.zero_slots(state.view(1, 8, -1), slots)
     rate = torch.tensor(c["rates"], dtype=torch.float32, device=DEV) if c["rot"] else None
     qs = [torch.empty(n, c["QC"], dtype=dtype, device=DEV) for n in c["lengths"]]
@@ -212,7 +212,7 @@ def _attention_case(seed, H, G, D, DV, T, window, keep, stand_out=None):
     return q, k, v
 
 
-def _run_attention(q, k, v, window, keep, scale, lam, out_scale, eps, gate, rows_form, dtype=torch.float32, split=None):
+def _run_attention(q, k, v, window, keep, scale, lam, out_scale, eps, gate, rows_form, dtype=torch.float32, split=None, shares=1):
     """Through the kernel: keys and values are placed in scattered pages first.  split: the step brings the rows from
     `split` on (the earlier ones are held)."""
     from catena_models_b200 import kernels
@@ -233,7 +233,9 @@ def _run_attention(q, k, v, window, keep, scale, lam, out_scale, eps, gate, rows
     qq = q[first:].reshape(T - first, -1).to(DEV, dtype).contiguous()
     ctx = torch.empty(T - first, H * DV, dtype=dtype, device=DEV)
     gg = gate[first:].to(DEV, dtype).contiguous() if gate is not None else None
-    kernels.diff_attn(ctx, qq, gg, pool, pool.shape[1], ptab, b, H, G, D, DV, window, keep, scale, lam, out_scale, eps, rows_form)
+    parts = torch.full(((T - first) * H * shares * (4 + 2 * DV),), float("nan"), device=DEV) if shares > 1 else None
+    kernels.diff_attn(ctx, qq, gg, pool, pool.shape[1], ptab, b, H, G, D, DV, window, keep, scale, lam, out_scale, eps, rows_form,
+                      parts=parts, splits=shares)
     return ctx
 
 
@@ -250,6 +252,8 @@ def test_two_maps_over_the_cache(H, G, D, DV, T, window, keep):
         _close(_run_attention(q, k, v, window, keep, scale, lam, 1 - diff, eps, gate, rows_form), ref, 2e-5)
         for split in (1, 33, T - 2, T - 1):                 # rows on top of held ones, down to the last alone
             _close(_run_attention(q, k, v, window, keep, scale, lam, 1 - diff, eps, gate, rows_form, split=split), ref[split:], 2e-5)
+    for shares in (2, 3, 16):                               # a row's keys cut over several blocks, more than it has tiles too
+        _close(_run_attention(q, k, v, window, keep, scale, lam, 1 - diff, eps, gate, True, split=T - 9, shares=shares), ref[T - 9:], 2e-5)
     bf = _run_attention(q, k, v, window, keep, scale, lam, 1 - diff, eps, gate, False, dtype=torch.bfloat16)
     _close(bf, ref, 0.05)
 
