@@ -17,6 +17,7 @@
 // code.  (The cache keeps every position: a window with kept first tokens is not a ring.)
 // Rows whose tok_seq is negative are padding: they touch nothing.
 #include "common.cuh"
+#include "diffattn.h"
 #include <math.h>
 
 struct TapRotArgs {
@@ -158,22 +159,6 @@ extern "C" int cm_tap_rotate_store(int dt, const TapRotArgs* args, cudaStream_t 
 }
 
 // ================================================================================ the two maps
-struct DiffAttnArgs {
-    void* ctx;                   // [T][ldc]: H heads of DV channels
-    long long ldc;
-    const void* q;               // [T][ldq]: H heads of [map 1 | map 2], D channels each
-    long long ldq;
-    const void* gate;            // [T][ldg]: a logit per head, or null
-    long long ldg;
-    const void* pool;
-    long long pages;
-    const int* ptab;
-    long long ptab_stride;
-    const int *tok_seq, *tok_pos, *seq_start, *seq_pos0, *seq_slot;
-    int T, B, H, G, D, DV, HDC, window, keep;
-    float scale, lambda, out_scale, eps;
-};
-
 __device__ __forceinline__ bool da_visible(int kpos, int qpos, int window, int keep) {
     return kpos <= qpos && (window <= 0 || qpos - kpos < window || kpos < keep);
 }

@@ -58,6 +58,7 @@ _SIGNATURES = {
     "cm_relu2_inplace": [_i, _vp, _ll, _vp],
     "cm_tap_rotate_store": [_i, _vp, _vp],
     "cm_diff_attn": [_i, _vp, _i, _i, _vp, _i, _vp],
+    "cm_diff_attn_mma": [_vp, _i, _vp],
     "cm_concat_cast": [_i, _vp, _vp, _vp, _ll, _i, _vp],
     "cm_shift_mix": [_i, _vp, _vp, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _i, _ll, _i, _vp],
     "cm_lowrank_decay": [_i, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _vp],
@@ -940,14 +941,15 @@ def diff_attn_splits(rows, H, keys, sm_count=148):
 
 
 def diff_attn(ctx, q, gate, pool, pages, ptab, batch, H, G, D, DV, window, keep, scale, lam, out_scale, eps, rows_form,
-              parts=None, splits=1):
+              parts=None, splits=1, tensor_cores=False):
     """Attention whose output is the difference of two softmax maps over the same values, read from the paged
     cache: q [T, H * 2 * D] (per head map 1, then map 2), ctx [T, H * DV]; a key at j is visible from i when
     j <= i and (i - j < window or j < keep) (window <= 0: all j <= i); o = a1 - lam * a2, brought to unit root mean
     square per head, times out_scale and sigmoid(gate[t, head]) (gate may be None).  `rows_form`: a block per row
     and head (steps of one token a sequence), whose visible keys may be cut into `splits` shares with float32 scratch
     `parts` of at least T * H * splits * (4 + 2 DV) elements between two launches; else tiles of queries, launched for
-    batch.max_len rows a sequence."""
+    batch.max_len rows a sequence, on the tensor cores with `tensor_cores` (bfloat16, head sizes that are multiples of 16
+    up to 128: `diff_attn_mma_fits`)."""
     if splits > 1 and (parts is None or parts.dtype != torch.float32 or parts.numel() < T_need(q, H, splits, DV)):
         raise KernelError("diff_attn: the shares' scratch is missing or too small")
     T = q.shape[0]
@@ -959,9 +961,21 @@ def diff_attn(ctx, q, gate, pool, pages, ptab, batch, H, G, D, DV, window, keep,
                       seq_start=_ptr(batch.seq_start), seq_pos0=_ptr(batch.seq_pos0), seq_slot=_ptr(batch.seq_slot), T=T,
                       B=batch.B, H=H, G=G, D=D, DV=DV, HDC=pool.shape[-1], window=window, keep=keep, scale=scale, lam=lam,
                       out_scale=out_scale, eps=eps)
+    if tensor_cores and not rows_form:
+        if q.dtype != torch.bfloat16:
+            raise KernelError("diff_attn: the tensor-core form takes bfloat16")
+        _check(lib().cm_diff_attn_mma(ctypes.byref(a), batch.max_len, _stream()), "diff_attn_mma",
+               cost=lambda: _diff_attn_cost(batch, T, H, G, D, DV, window, keep, q.element_size(), rows_form))
+        return
     _check(lib().cm_diff_attn(dtype_code(q.dtype), ctypes.byref(a), int(rows_form), batch.max_len, _ptr(parts), splits,
                               _stream()), "diff_attn", 2 if rows_form and splits > 1 else 1,
            cost=lambda: _diff_attn_cost(batch, T, H, G, D, DV, window, keep, q.element_size(), rows_form))
+
+
+def diff_attn_mma_fits(D, DV, H, q_row, cache_entry):
+    """True if the tensor-core tiles form takes these sizes (key and value heads, heads, elements of a query row and of a
+    cache entry)."""
+    return D % 16 == 0 and DV % 16 == 0 and 0 < D <= 128 and 0 < DV <= 128 and q_row % 8 == 0 and cache_entry % 8 == 0
 
 
 def T_need(q, H, splits, DV):

@@ -108,7 +108,9 @@ class DiffAttention(Mixer):
                 parts = rt.scratch("diff_attn_parts", batch.T * H * splits * (4 + 2 * DV))
         kernels.diff_attn(ctx, q, proj[:, self.channels:], kv.pool, kv.pages, kv.ptab, batch, H, G, D, DV, self.window,
                           self.keep_first, self.scale, self.lam, 1.0 - self.diff, self.eps, rows_form=one_each,
-                          parts=parts, splits=splits)
+                          parts=parts, splits=splits,
+                          tensor_cores=(not one_each and x.dtype == torch.bfloat16 and rt.tensor_core_prompts
+                                        and kernels.diff_attn_mma_fits(D, DV, H, self.q_size, self.cache_head)))
         return self.out.apply(rt, ctx, out_dtype=self.out_dtype)
 
 

@@ -212,7 +212,8 @@ def _attention_case(seed, H, G, D, DV, T, window, keep, stand_out=None):
     return q, k, v
 
 
-def _run_attention(q, k, v, window, keep, scale, lam, out_scale, eps, gate, rows_form, dtype=torch.float32, split=None, shares=1):
+def _run_attention(q, k, v, window, keep, scale, lam, out_scale, eps, gate, rows_form, dtype=torch.float32, split=None, shares=1,
+                   tensor_cores=False):
     """Through the kernel: keys and values are placed in scattered pages first.  split: the step brings the rows from
     `split` on (the earlier ones are held)."""
     from catena_models_b200 import kernels
@@ -235,7 +236,7 @@ def _run_attention(q, k, v, window, keep, scale, lam, out_scale, eps, gate, rows
     gg = gate[first:].to(DEV, dtype).contiguous() if gate is not None else None
     parts = torch.full(((T - first) * H * shares * (4 + 2 * DV),), float("nan"), device=DEV) if shares > 1 else None
     kernels.diff_attn(ctx, qq, gg, pool, pool.shape[1], ptab, b, H, G, D, DV, window, keep, scale, lam, out_scale, eps, rows_form,
-                      parts=parts, splits=shares)
+                      parts=parts, splits=shares, tensor_cores=tensor_cores)
     return ctx
 
 
@@ -258,22 +259,47 @@ def test_two_maps_over_the_cache(H, G, D, DV, T, window, keep):
     _close(bf, ref, 0.05)
 
 
-@pytest.mark.parametrize("rows_form", [False, True])
+@pytest.mark.parametrize("H, G, D, DV, T, window, keep", [
+    (4, 2, 16, 16, 150, 9, 3), (3, 1, 32, 48, 200, 70, 0), (2, 2, 48, 96, 330, 40, 20), (2, 1, 64, 128, 260, 64, 32),
+    (2, 1, 128, 64, 140, 0, 0), (1, 1, 16, 32, 66, 1, 1), (2, 2, 80, 112, 200, 130, 70)])
+def test_two_maps_on_the_tensor_cores(H, G, D, DV, T, window, keep):
+    """The bfloat16 tiles form on mma.sync against the plain statement on the same bfloat16 inputs: what is left is the
+    output's own rounding."""
+    q, k, v = (t.to(torch.bfloat16).float() for t in _attention_case(16, H, G, D, DV, T, window, keep))
+    gate = torch.randn(T, H, generator=torch.Generator().manual_seed(17)).to(torch.bfloat16).float()
+    scale, lam, diff, eps = D ** -0.5, 0.45, 0.2, 1e-5
+    ref = plain.difference_attention_heads(q.double(), k.double(), v.double(), scale, window or T + 1, keep, lam, diff, eps)
+    ref = (ref * torch.sigmoid(gate.double())[:, :, None]).reshape(T, H * DV)
+    for split in (None, 1, 63, 64, T - 2):
+        got = _run_attention(q, k, v, window, keep, scale, lam, 1 - diff, eps, gate, False, dtype=torch.bfloat16, split=split,
+                             tensor_cores=True)
+        _close(got, ref[split or 0:], 6e-3)
+        err = (got.double().cpu() - ref[split or 0:]).abs() / ref.abs().max()
+        assert float(err.mean()) < 1e-3                       # rounding of the output alone: a bfloat16 weight would show
+
+
+@pytest.mark.parametrize("form", ["tiles", "rows", "mma"])
 @pytest.mark.parametrize("window, keep, T", [(40, 20, 300), (9, 3, 70), (64, 0, 200), (33, 40, 129)])
-def test_a_key_at_every_edge_decides_the_row(window, keep, T, rows_form):
+def test_a_key_at_every_edge_decides_the_row(window, keep, T, form):
     """The last query's score with one key dwarfs the rest: just inside the window, just outside it, the last kept
     token, the first token that is not kept, a far key at a page border.  A mask that is one token off moves the result
     from one value row to another."""
-    H, G, D, DV = 2, 1, 16, 8
+    H, G, D, DV = 2, 1, 16, 16
+    rows_form, mma = form == "rows", form == "mma"
+    dtype, tol = (torch.bfloat16, 8e-3) if mma else (torch.float32, 2e-5)
     qi = T - 1
     spots = [qi - window + 1, qi - window, qi - window - 1, keep - 1, keep, 0, 63, 64, qi]
     for kj in spots:
         if not 0 <= kj <= qi:
             continue
         q, k, v = _attention_case(8, H, G, D, DV, T, window, keep, stand_out=(qi, kj))
+        if mma:
+            q, k, v = (t.to(torch.bfloat16).float() for t in (q, k, v))
         ref = plain.difference_attention_heads(q.double(), k.double(), v.double(), 1.0, window, keep, 0.1, 0.0, 1e-6)
-        got = _run_attention(q, k, v, window, keep, 1.0, 0.1, 1.0, 1e-6, None, rows_form, split=T - 1 if rows_form else None)
-        _close(got[-1], ref[-1].reshape(-1), 2e-5)
+        got = _run_attention(q, k, v, window, keep, 1.0, 0.1, 1.0, 1e-6, None, rows_form, split=T - 1 if rows_form else None,
+                             dtype=dtype, tensor_cores=mma)
+        _close(got[-1], ref[-1].reshape(-1), tol)
         # and the same query in a prompt's portion
-        got = _run_attention(q, k, v, window, keep, 1.0, 0.1, 1.0, 1e-6, None, rows_form, split=max(0, T - 37))
-        _close(got[-1], ref[-1].reshape(-1), 2e-5)
+        got = _run_attention(q, k, v, window, keep, 1.0, 0.1, 1.0, 1e-6, None, rows_form, split=max(0, T - 37), dtype=dtype,
+                             tensor_cores=mma)
+        _close(got[-1], ref[-1].reshape(-1), tol)
