@@ -17,6 +17,7 @@
 // Beside it: the token shift (each projection reads its own blend of the present and the previous
 // token's input), the low-rank decay network, and the capped gate pre-activations.
 #include "common.cuh"
+#include "recurrent.h"
 #include <math.h>
 
 // ------------------------------------------------------------------------------ token shift
@@ -220,27 +221,6 @@ extern "C" int cm_capped_gates(int dt, float* out, const void* x, const void* w,
 }
 
 // ------------------------------------------------------------------------------ the scan
-struct ScanArgs {
-    const void *q, *k, *v, *g;        // query (or receptance), key, value, output-gate pre-activation: activation rows
-    long long ldq, ldk, ldv, ldg;     // row pitches, elements
-    const float* decay;               // MODE 0: [rows][H * D] per-channel decay;  MODE 1: [rows][2 H] log gates (i, then f)
-    const float* bonus;               // MODE 0: [H][D]
-    const float* norm_w;              // [H * DV]
-    void* out;                        // [rows][H * DV], pitch ldo
-    long long ldo;
-    float* state;                     // [slots][state_stride]; this mixer's part starts at state_offset
-    long long state_stride, state_offset;
-    const void* shift_src;            // MODE 0: the mixer's input rows [rows][W]; the last one is kept as the next step's
-    int W;                            //         previous input, at the head of the state row (null: nothing kept)
-    const int *seq_start, *seq_slot;
-    int H, D, DV, KS;
-    float q_scale, eps;
-    float* raw;                       // [rows][H * DV] float: the heads' outputs before norm and gate
-    long long rows;
-    int qkv_act;                      // MODE 2: 1 = q, k and v pass through silu (in float) as they are staged
-    int norm_all_heads;               // 1: the unit norm runs over all heads of a row together, not head by head
-};
-
 #define SCAN_THREADS 128
 #define SCAN_MAX_ROWS 32          // rows of the step that a block stages at a time
 
@@ -491,6 +471,23 @@ head_norm_gate_kernel(const ScanArgs a) {
         const float act = MODE == 0 ? gz * sigmoid_f32(gz) : sigmoid_f32(gz);
         O[c] = from_f32<T>(((r[c] * inv) * a.norm_w[hd * DV + c]) * act);
     }
+}
+
+// The unit norm, channel weights and gate over `raw` (see head_norm_gate_kernel): act 0 silu, 1 sigmoid.
+int cm_scan_norm_gate(int dt, int act, const ScanArgs& a, cudaStream_t st) {
+    ScanArgs n = a;
+    if (a.norm_all_heads) {                      // the norm over all heads of a row together is the norm of one head that spans the row
+        n.DV = a.H * a.DV;
+        n.H = 1;
+    }
+    dim3 egrid((unsigned)((n.rows * n.H + 3) / 4));
+    if (dt == DT_F32 && act == 0) cm_launch(head_norm_gate_kernel<float, 0>, egrid, 128, 0, st, n);
+    else if (dt == DT_F32) cm_launch(head_norm_gate_kernel<float, 1>, egrid, 128, 0, st, n);
+    else if (dt == DT_BF16 && act == 0) cm_launch(head_norm_gate_kernel<bf16, 0>, egrid, 128, 0, st, n);
+    else if (dt == DT_BF16) cm_launch(head_norm_gate_kernel<bf16, 1>, egrid, 128, 0, st, n);
+    else return CM_ERR_DTYPE;
+    CM_CHECK_LAUNCH();
+    return CM_OK;
 }
 
 // mode 0: decay mix, mode 1: matrix memory, mode 2: constant decay per head.  B sequences; rows of the step are found

@@ -66,6 +66,7 @@ _SIGNATURES = {
     "cm_tanh_inplace": [_i, _vp, _ll, _vp],
     "cm_decay_from_logits": [_vp, _vp, _vp, _ll, _i, _vp],
     "cm_matrix_scan": [_i, _i, _vp, _i, _vp],
+    "cm_lightning_chunked": [_i, _vp, _i, _i, _vp, _vp],
     "cm_moe_route": [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _i, _vp, _i, _vp],
     "cm_moe_gather": [_i, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _vp],
     "cm_gemm_tc_grouped": [_i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _vp, _i, _vp, _vp],
@@ -849,14 +850,16 @@ class _ScanArgs(ctypes.Structure):
 
 
 def matrix_scan(mode, out, q, k, v, g, decay, bonus, norm_w, state, state_offset, seq_start, seq_slot, B, H, D, DV,
-                q_scale, eps, shift_src=None, qkv_silu=False, norm_all_heads=False):
+                q_scale, eps, shift_src=None, qkv_silu=False, norm_all_heads=False, chunk_scratch=None, max_len=0):
     """The recurrence of a mixer with a matrix state per head over the step's rows of B sequences, with the
     heads' unit norm, channel weights and output gate.  mode "decay": o = (S + diag(bonus) k v^T)^T q, then
     S <- diag(decay_t) S + k v^T (decay float32 [rows, H D]; gate silu(g)).  mode "memory": log-domain
     gates with a running maximum and a normaliser (decay float32 [rows, 2 H]: i, then f; gate sigmoid(g)).
     mode "constant": S <- w S + k v^T, o = S^T q with one decay per head (decay float32 [H]; gate sigmoid(g));
     `qkv_silu`: q, k and v pass through silu as they are read.  `norm_all_heads`: the unit norm runs over all
-    heads of a row together.
+    heads of a row together.  `chunk_scratch` (mode "constant"; float32, at least `lightning_scratch_floats` elements for
+    sequences of up to `max_len` rows): the prompt form, which regroups the sums into chunks of 64 rows so that only the
+    state's step from chunk to chunk is serial (csrc/lightning.cu); the numbers agree with the scan's beyond rounding.
     q, k [rows, H D], v, g, out [rows, H DV]: activation dtype, any row pitch.  state: float32 [slots, n];
     this mixer's part of a row starts at `state_offset`.  `shift_src` [rows, W] (mode "decay"): its last
     row of each sequence is kept at the head of the state row."""
@@ -873,11 +876,34 @@ def matrix_scan(mode, out, q, k, v, g, decay, bonus, norm_w, state, state_offset
                   norm_all_heads=int(norm_all_heads))
     if mode == "constant" and (decay.dtype != torch.float32 or decay.numel() != H):
         raise KernelError("matrix_scan: mode 'constant' takes one float32 decay per head")
+    if chunk_scratch is not None:
+        if mode != "constant" or chunk_scratch.dtype != torch.float32 or chunk_scratch.numel() < lightning_scratch_floats(B, max_len, H, D, DV):
+            raise KernelError("matrix_scan: the chunked form is for mode 'constant' and needs its float32 scratch")
+        _check(lib().cm_lightning_chunked(dtype_code(out.dtype), ctypes.byref(a), B, max_len, _ptr(chunk_scratch), _stream()),
+               "lightning_chunked", 4,
+               cost=lambda: (f"{B} sequences, {rows} rows, {H} heads of {D}x{DV}", _nbytes(q, k, v, g, out) + 2 * B * H * D * DV * 4,
+                             6 * rows * H * D * DV))
+        return
     _check(lib().cm_matrix_scan(dtype_code(out.dtype), {"decay": 0, "memory": 1, "constant": 2}[mode], ctypes.byref(a), B, _stream()),
            "matrix_scan_" + mode, 2,
            cost=lambda: (f"{B} sequences, {rows} rows, {H} heads of {D}x{DV}",
                          _nbytes(q, k, v, g, out) + (0 if decay is None or decay.dim() < 2 else rows * decay.shape[1] * 4) + 2 * B * H * D * DV * 4,
                          6 * rows * H * D * DV))
+
+
+LIGHTNING_CHUNK = 64               # csrc/lightning.cu: rows of a chunk of the prompt form
+
+
+def lightning_scratch_floats(B, max_len, H, D, DV):
+    """Floats of scratch that the chunked prompt form needs: a state per chunk, head and sequence."""
+    return B * -(-max_len // LIGHTNING_CHUNK) * H * D * DV
+
+
+def lightning_chunked_fits(D, DV):
+    """True if heads of D x DV fit the chunked form's shared memory."""
+    fn = lib().cm_lightning_chunked_smem
+    fn.argtypes, fn.restype = [_i, _i], _ll
+    return fn(D, DV) <= 200 * 1024
 
 
 # ------------------------------------------------------------------ attention as a difference of two maps

@@ -154,6 +154,8 @@ class ConstantDecayMemory(Mixer):
     weight and sigmoid(W_g h), then the output projection.  State per sequence: S, float32."""
     prompt_capturable = True
     supports_append = True
+    CHUNKED_MIN_ROWS = 128                  # shorter steps run the serial scan
+    CHUNKED_MAX_SCRATCH = 256 << 20         # bytes of per-chunk states above which a step runs the serial scan
 
     def __init__(self, prefix, hidden, heads, dim, value_dim, decay, eps, out_dtype=None):
         if len(decay) != heads:
@@ -184,10 +186,17 @@ class ConstantDecayMemory(Mixer):
         T, KS, VS = batch.T, self.k_size, self.v_size
         proj = self.qkvg.apply(rt, x)
         o = torch.empty((T, VS), dtype=x.dtype, device=x.device)
+        # prompts: the chunked form, unless its per-chunk states would take more scratch than a step is worth (many
+        # long prompts at once, which give the serial scan enough independent work anyway)
+        scratch = None
+        if batch.kind != "decode" and batch.max_len >= self.CHUNKED_MIN_ROWS and kernels.lightning_chunked_fits(self.dim, self.value_dim):
+            need = kernels.lightning_scratch_floats(batch.B, batch.max_len, self.heads, self.dim, self.value_dim)
+            if need * 4 <= self.CHUNKED_MAX_SCRATCH:
+                scratch = rt.scratch("lightning_chunks", need)
         kernels.matrix_scan("constant", o, proj[:, :KS], proj[:, KS:2 * KS], proj[:, 2 * KS:2 * KS + VS],
                             proj[:, 2 * KS + VS:], self.decay, None, self.norm_w, state.tensor, 0, batch.seq_start,
                             batch.seq_slot, batch.B, self.heads, self.dim, self.value_dim, 1.0, self.eps,
-                            qkv_silu=True, norm_all_heads=True)
+                            qkv_silu=True, norm_all_heads=True, chunk_scratch=scratch, max_len=batch.max_len)
         return self.out.apply(rt, o, out_dtype=self.out_dtype)
 
 

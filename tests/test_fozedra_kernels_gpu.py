@@ -66,12 +66,14 @@ def test_squared_relu():
         _close(a, ref, 1e-6 if dtype == torch.float32 else 5e-3)
 
 
-@pytest.mark.parametrize("H, D, DV", [(2, 16, 24), (1, 12, 20), (3, 4, 12), (4, 64, 32)])
-def test_constant_decay_scan_whole_portions_and_slots(H, D, DV):
+@pytest.mark.parametrize("chunked", [False, True])
+@pytest.mark.parametrize("H, D, DV", [(2, 16, 24), (1, 12, 20), (3, 4, 12), (4, 64, 32), (2, 7, 9)])
+def test_constant_decay_scan_whole_portions_and_slots(H, D, DV, chunked):
+    """`chunked`: the prompt form that regroups the sums into chunks of 64 rows, against the same plain statement."""
     from catena_models_b200 import kernels
 
     g = torch.Generator().manual_seed(3)
-    lengths = [45, 1, 70]
+    lengths = [45, 1, 70] if not chunked else [200, 1, 129]
     T = sum(lengths)
     q, k, v, gate = (torch.randn(T, n, generator=g) for n in (H * D, H * D, H * DV, H * DV))
     decay = torch.tensor([0.6 + 0.39 * (i + 1) / H for i in range(H)])
@@ -84,7 +86,7 @@ def test_constant_decay_scan_whole_portions_and_slots(H, D, DV):
                                   s(v[lo:hi].double()).view(-1, H, DV), decay.double()).reshape(hi - lo, H * DV)
         return plain.rms_unit(o, eps) * norm_w.double() * torch.sigmoid(gate[lo:hi].double())
 
-    bounds = [0, 45, 46, 116]
+    bounds = [0, lengths[0], lengths[0] + 1, T]
     ref = torch.cat([reference(bounds[i], bounds[i + 1]) for i in range(3)])
     state = torch.full((5, H * D * DV), float("nan"), device=DEV)
     dq, dk, dv, dg = (t.to(DEV) for t in (q, k, v, gate))
@@ -106,14 +108,18 @@ def test_constant_decay_scan_whole_portions_and_slots(H, D, DV):
             idx = torch.tensor(rows, device=DEV)
             b = _batch(lens, [0] * len(lens), sl)
             o = torch.empty(len(rows), H * DV, device=DEV)
+            scratch = None
+            if chunked:
+                scratch = torch.full((kernels.lightning_scratch_floats(b.B, b.max_len, H, D, DV),), float("nan"), device=DEV)
             kernels.matrix_scan("constant", o, dq[idx], dk[idx], dv[idx], dg[idx], decay.to(DEV), None, norm_w.to(DEV), state, 0,
-                                b.seq_start, b.seq_slot, b.B, H, D, DV, 1.0, eps, qkv_silu=True, norm_all_heads=True)
+                                b.seq_start, b.seq_slot, b.B, H, D, DV, 1.0, eps, qkv_silu=True, norm_all_heads=True,
+                                chunk_scratch=scratch, max_len=b.max_len)
             out[idx] = o
         return out
 
     _close(run([1000, 1000, 1000], [0, 1, 2]), ref, 2e-5)
     _close(run([7, 1, 33], [4, 2, 0]), ref, 2e-5)            # portions; the slots of before, used again
-    _close(run([2, 1, 1], [1, 0, 3]), ref, 2e-5)             # two tokens, and token by token
+    _close(run([65, 1, 64] if chunked else [2, 1, 1], [1, 0, 3]), ref, 2e-5)     # chunk borders; or two tokens and token by token
 
 
 def _taps_case(seed, H, G, D, DV, K, rot, lengths):
