@@ -31,8 +31,28 @@ __device__ __forceinline__ float lc_in(const T* p, bool act) {
 // rows [t0, t0 + n) of operand `src` (row pitch ld, head offset applied) as floats into dst[r * pitch + c]; columns
 // from `width` to `pitch` and rows from n to LC hold zeros.  `scale_rows`: row r is multiplied by pw[n - 1 - r].
 template <typename T>
+__device__ __forceinline__ bool lc_vec8(const T* src, long long ld, int width) {
+    return width % 8 == 0 && ld % 8 == 0 && (((uintptr_t)src) & 15) == 0;
+}
+
+template <typename T>
 __device__ __forceinline__ void lc_stage(float* dst, int pitch, const T* src, long long ld, int n, int width, bool act,
                                          const float* pw, bool scale_rows) {
+    if (lc_vec8<T>(src, ld, width)) {            // 16-byte loads: width = pitch here (a multiple of 8)
+        const int w8 = width >> 3;
+        for (int e = threadIdx.x; e < LC * w8; e += LT) {
+            const int r = e / w8, c = (e - r * w8) << 3;
+            float x[8] = {};
+            if (r < n) {
+                load8f<T>(src + r * ld + c, x);
+                const float f = scale_rows ? pw[n - 1 - r] : 1.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) x[i] = (act ? x[i] * sigmoid_f32(x[i]) : x[i]) * f;
+            }
+            store8f<float>(dst + r * pitch + c, x);
+        }
+        return;
+    }
     for (int e = threadIdx.x; e < LC * pitch; e += LT) {
         const int r = e / pitch, c = e - r * pitch;
         float x = 0.f;
@@ -47,6 +67,22 @@ __device__ __forceinline__ void lc_stage(float* dst, int pitch, const T* src, lo
 // the same, transposed: dst[c * LC + r]; neighbouring threads take neighbouring rows
 template <typename T>
 __device__ __forceinline__ void lc_stage_t(float* dst, int pitch, const T* src, long long ld, int n, int width, bool act) {
+    if (lc_vec8<T>(src, ld, width)) {            // a thread takes eight channels of its row; a warp's stores go to 32 banks
+        for (int e = threadIdx.x; e < LC * (width >> 3); e += LT) {
+            const int c = (e / LC) << 3, r = e % LC;
+            float x[8] = {};
+            if (r < n) {
+                load8f<T>(src + r * ld + c, x);
+                if (act) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) x[i] *= sigmoid_f32(x[i]);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dst[(c + i) * LC + r] = x[i];
+        }
+        return;
+    }
     for (int e = threadIdx.x; e < LC * pitch; e += LT) {
         const int c = e / LC, r = e - c * LC;
         dst[e] = (r < n && c < width) ? lc_in<T>(src + r * ld + c, act) : 0.f;
@@ -112,12 +148,21 @@ lightning_carry_kernel(const ScanArgs a, ChunkGeom geo, float* __restrict__ scra
     float* st = a.state + (long long)a.seq_slot[b] * a.state_stride + a.state_offset + hd * per + e;
     const float w = a.decay[hd], w_full = powf(w, (float)LC);
     float S = *st;
-    for (int j = 0; j * LC < len; ++j) {
-        float* slot = scratch + (((long long)b * geo.chunks + j) * a.H + hd) * per + e;
-        const float kv = *slot;
-        *slot = S;
-        const int n = min(LC, len - j * LC);
-        S = fmaf(n == LC ? w_full : powf(w, (float)n), S, kv);
+    const long long step = (long long)a.H * per;                    // from a chunk's slot to the next chunk's
+    float* slot = scratch + ((long long)b * geo.chunks * a.H + hd) * per + e;
+    const int n_chunks = (len + LC - 1) / LC;
+    for (int j0 = 0; j0 < n_chunks; j0 += 8) {                      // eight chunks' sums are asked for at once
+        float kv[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) kv[u] = j0 + u < n_chunks ? slot[(j0 + u) * step] : 0.f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (j0 + u < n_chunks) {
+                slot[(j0 + u) * step] = S;
+                const int n = min(LC, len - (j0 + u) * LC);
+                S = fmaf(n == LC ? w_full : powf(w, (float)n), S, kv[u]);
+            }
+        }
     }
     *st = S;
 }
