@@ -309,7 +309,7 @@ diff_attn_tile_kernel(const DiffAttnArgs a) {
 }
 
 // -------------------------------------------------------------------------------- a row at a time
-// One block = one row (token), one head and one share of the row's visible keys: the tiles of 32 keys that hold
+// One block = one row (token), one head (or four heads of one key/value head) and one share of the row's visible keys: the tiles of 32 keys that hold
 // kept first tokens or lie in the row's window are dealt out in turns to the warps of `splits` blocks.  Each warp
 // keeps running maxima and sums of its own; a block merges its warps in warp order, and (with more than one
 // share) leaves maxima, sums and value sums in `parts`, which diff_attn_merge_kernel adds in share order.  A lane is
@@ -317,50 +317,66 @@ diff_attn_tile_kernel(const DiffAttnArgs a) {
 // of channels for the value sums.
 #define DR_WARPS 4
 
-template <typename T>
-__device__ __forceinline__ void da_key_dots(const T* kr, const float* Qs, int D, bool vec, float& s1, float& s2) {
-    s1 = s2 = 0.f;
+// a key row [map 1 | map 2] against R heads' query vectors (Qs: R rows of 2 D floats)
+template <typename T, int R>
+__device__ __forceinline__ void da_key_dots(const T* kr, const float* Qs, int D, bool vec, float* s1, float* s2) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) s1[r] = s2[r] = 0.f;
     if (vec) {
         for (int d = 0; d < D; d += 8) {
             float k1[8], k2[8];
             load8f<T>(kr + d, k1);
             load8f<T>(kr + D + d, k2);
 #pragma unroll
-            for (int x = 0; x < 8; ++x) {
-                s1 = fmaf(Qs[d + x], k1[x], s1);
-                s2 = fmaf(Qs[D + d + x], k2[x], s2);
+            for (int r = 0; r < R; ++r) {
+                const float* q = Qs + r * 2 * D;
+#pragma unroll
+                for (int x = 0; x < 8; ++x) {
+                    s1[r] = fmaf(q[d + x], k1[x], s1[r]);
+                    s2[r] = fmaf(q[D + d + x], k2[x], s2[r]);
+                }
             }
         }
     } else {
         for (int d = 0; d < D; ++d) {
-            s1 = fmaf(Qs[d], to_f32(kr[d]), s1);
-            s2 = fmaf(Qs[D + d], to_f32(kr[D + d]), s2);
+            const float k1 = to_f32(kr[d]), k2 = to_f32(kr[D + d]);
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                s1[r] = fmaf(Qs[r * 2 * D + d], k1, s1[r]);
+                s2[r] = fmaf(Qs[r * 2 * D + D + d], k2, s2[r]);
+            }
         }
     }
 }
 
-template <typename T, int NJ>
+// R: query heads of one key/value head that a block takes together (they read the same keys and values).
+template <typename T, int NJ, int R>
 __global__ void __launch_bounds__(DR_WARPS * 32)
 diff_attn_row_kernel(const DiffAttnArgs a, float* __restrict__ parts, int splits) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float smem[];
     const int D2 = 2 * a.D, DV = a.DV;
-    float* Qs = smem;                            // [2D]
-    float* Ms = Qs + D2;                         // [DR_WARPS][4]: m1, l1, m2, l2
-    float* As = Ms + DR_WARPS * 4;               // [DR_WARPS][2][DV]
+    float* Qs = smem;                            // [R][2D]
+    float* Ms = Qs + R * D2;                     // [DR_WARPS][R][4]: m1, l1, m2, l2
+    float* As = Ms + DR_WARPS * R * 4;           // [DR_WARPS][R][2][DV]
     const long long t = blockIdx.y;
-    const int h = blockIdx.x, g = h / (a.H / a.G), share = blockIdx.z;
+    const int h0 = blockIdx.x * R, g = h0 / (a.H / a.G), share = blockIdx.z;
     const int b = a.tok_seq[t];
     if (b < 0) return;
     const int qpos = a.tok_pos[t];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int* prow = a.ptab + (long long)a.seq_slot[b] * a.ptab_stride;
-    for (int d = threadIdx.x; d < D2; d += DR_WARPS * 32) Qs[d] = to_f32(((const T*)a.q)[t * a.ldq + (long long)h * D2 + d]);
+    for (int d = threadIdx.x; d < R * D2; d += DR_WARPS * 32) Qs[d] = to_f32(((const T*)a.q)[t * a.ldq + (long long)h0 * D2 + d]);
     __syncthreads();
-    float m1 = -INFINITY, m2 = -INFINITY, l1 = 0.f, l2 = 0.f, acc1[NJ], acc2[NJ];
+    float m1[R], m2[R], l1[R], l2[R], acc1[R][NJ], acc2[R][NJ];
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) acc1[j] = acc2[j] = 0.f;
+    for (int r = 0; r < R; ++r) {
+        m1[r] = m2[r] = -INFINITY;
+        l1[r] = l2[r] = 0.f;
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) acc1[r][j] = acc2[r][j] = 0.f;
+    }
     const int last_tile = qpos / 32;
     const int kept_tiles = a.window > 0 ? min((min(a.keep, qpos + 1) + 31) / 32, last_tile + 1) : 0;
     const int win_tile = a.window > 0 ? max(kept_tiles, max(0, qpos - a.window + 1) / 32) : 0;
@@ -370,99 +386,116 @@ diff_attn_row_kernel(const DiffAttnArgs a, float* __restrict__ parts, int splits
         const int tile = idx < kept_tiles ? idx : win_tile + idx - kept_tiles;
         const int kpos = tile * 32 + lane;
         const bool vis = da_visible(kpos, qpos, a.window, a.keep);
-        const int page = kpos <= qpos ? prow[kpos / PAGE_TOKENS] : 0;
-        float s1 = 0.f, s2 = 0.f;
-        if (vis)
-            da_key_dots<T>(kv_tile((const T*)a.pool, 0, a.pages, page, g, a.G, a.HDC) + (long long)(kpos % PAGE_TOKENS) * a.HDC,
-                           Qs, a.D, vec, s1, s2);
-        s1 = vis ? s1 * a.scale : -INFINITY;
-        s2 = vis ? s2 * a.scale : -INFINITY;
-        const float x1 = fmaxf(m1, warp_max(s1)), x2 = fmaxf(m2, warp_max(s2));
-        if (x1 == -INFINITY) continue;           // no key of this tile is seen (uniform over the warp)
-        const float p1 = vis ? expf(s1 - x1) : 0.f, p2 = vis ? expf(s2 - x2) : 0.f;
-        const float f1 = expf(m1 - x1), f2 = expf(m2 - x2);
-        l1 = l1 * f1 + warp_sum(p1);
-        l2 = l2 * f2 + warp_sum(p2);
-        m1 = x1;
-        m2 = x2;
-#pragma unroll
-        for (int j = 0; j < NJ; ++j) {
-            acc1[j] *= f1;
-            acc2[j] *= f2;
-        }
         const unsigned seen = __ballot_sync(0xffffffffu, vis);
+        if (!seen) continue;                     // no key of this tile is seen
+        const int page = kpos <= qpos ? prow[kpos / PAGE_TOKENS] : 0;
+        float s1[R], s2[R], p1[R], p2[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) s1[r] = s2[r] = 0.f;
+        if (vis)
+            da_key_dots<T, R>(kv_tile((const T*)a.pool, 0, a.pages, page, g, a.G, a.HDC) + (long long)(kpos % PAGE_TOKENS) * a.HDC,
+                              Qs, a.D, vec, s1, s2);
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const float v1 = vis ? s1[r] * a.scale : -INFINITY, v2 = vis ? s2[r] * a.scale : -INFINITY;
+            const float x1 = fmaxf(m1[r], warp_max(v1)), x2 = fmaxf(m2[r], warp_max(v2));
+            p1[r] = vis ? expf(v1 - x1) : 0.f;
+            p2[r] = vis ? expf(v2 - x2) : 0.f;
+            const float f1 = expf(m1[r] - x1), f2 = expf(m2[r] - x2);
+            l1[r] = l1[r] * f1 + warp_sum(p1[r]);
+            l2[r] = l2[r] * f2 + warp_sum(p2[r]);
+            m1[r] = x1;
+            m2[r] = x2;
+#pragma unroll
+            for (int j = 0; j < NJ; ++j) {
+                acc1[r][j] *= f1;
+                acc2[r][j] *= f2;
+            }
+        }
         // a tile of 32 keys lies within one page of 64
         const int tile_page = __shfl_sync(0xffffffffu, page, __ffs(seen) - 1);
         const T* vt = kv_tile((const T*)a.pool, 1, a.pages, tile_page, g, a.G, a.HDC) + (long long)((tile * 32) % PAGE_TOKENS) * a.HDC;
-#pragma unroll 4
+#pragma unroll 2
         for (int kk = 0; kk < 32; ++kk) {
             if (!((seen >> kk) & 1u)) continue;  // an unseen key's values may never have been written
-            const float q1 = __shfl_sync(0xffffffffu, p1, kk), q2 = __shfl_sync(0xffffffffu, p2, kk);
             const T* vr = vt + (long long)kk * a.HDC;
+            float v[NJ];
 #pragma unroll
-            for (int j = 0; j < NJ; ++j) {
-                const int d = lane + 32 * j;
-                const float v = d < DV ? to_f32(vr[d]) : 0.f;
-                acc1[j] = fmaf(q1, v, acc1[j]);
-                acc2[j] = fmaf(q2, v, acc2[j]);
+            for (int j = 0; j < NJ; ++j) v[j] = lane + 32 * j < DV ? to_f32(vr[lane + 32 * j]) : 0.f;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const float q1 = __shfl_sync(0xffffffffu, p1[r], kk), q2 = __shfl_sync(0xffffffffu, p2[r], kk);
+#pragma unroll
+                for (int j = 0; j < NJ; ++j) {
+                    acc1[r][j] = fmaf(q1, v[j], acc1[r][j]);
+                    acc2[r][j] = fmaf(q2, v[j], acc2[r][j]);
+                }
             }
         }
     }
-    if (lane == 0) {
-        Ms[warp * 4] = m1;
-        Ms[warp * 4 + 1] = l1;
-        Ms[warp * 4 + 2] = m2;
-        Ms[warp * 4 + 3] = l2;
-    }
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) {
-        const int d = lane + 32 * j;
-        if (d < DV) {
-            As[(warp * 2) * DV + d] = acc1[j];
-            As[(warp * 2 + 1) * DV + d] = acc2[j];
+    for (int r = 0; r < R; ++r) {
+        if (lane == 0) {
+            float* ms = Ms + (warp * R + r) * 4;
+            ms[0] = m1[r];
+            ms[1] = l1[r];
+            ms[2] = m2[r];
+            ms[3] = l2[r];
         }
-    }
-    __syncthreads();
-    if (warp != 0) return;
-    float M1 = -INFINITY, M2 = -INFINITY;
-    for (int w = 0; w < DR_WARPS; ++w) {
-        M1 = fmaxf(M1, Ms[w * 4]);
-        M2 = fmaxf(M2, Ms[w * 4 + 2]);
-    }
-    float L1 = 0.f, L2 = 0.f, o1[NJ], o2[NJ];
-#pragma unroll
-    for (int j = 0; j < NJ; ++j) o1[j] = o2[j] = 0.f;
-    for (int w = 0; w < DR_WARPS; ++w) {
-        if (Ms[w * 4] == -INFINITY) continue;    // a warp that saw no tile
-        const float f1 = expf(Ms[w * 4] - M1), f2 = expf(Ms[w * 4 + 2] - M2);
-        L1 = fmaf(Ms[w * 4 + 1], f1, L1);
-        L2 = fmaf(Ms[w * 4 + 3], f2, L2);
 #pragma unroll
         for (int j = 0; j < NJ; ++j) {
             const int d = lane + 32 * j;
             if (d < DV) {
-                o1[j] = fmaf(As[(w * 2) * DV + d], f1, o1[j]);
-                o2[j] = fmaf(As[(w * 2 + 1) * DV + d], f2, o2[j]);
+                As[((warp * R + r) * 2) * DV + d] = acc1[r][j];
+                As[((warp * R + r) * 2 + 1) * DV + d] = acc2[r][j];
             }
         }
     }
-    if (splits == 1) {
-        da_finish<T, NJ>(a, t, h, o1, o2, L1, L2);
-        return;
-    }
-    float* part = parts + ((t * a.H + h) * splits + share) * (long long)(4 + 2 * DV);
-    if (lane == 0) {
-        part[0] = M1;
-        part[1] = L1;
-        part[2] = M2;
-        part[3] = L2;
-    }
+    __syncthreads();
+    // warp w merges head w, w + DR_WARPS, ... of the block's heads over the warps' partial results, in warp order
+    for (int r = warp; r < R; r += DR_WARPS) {
+        float M1 = -INFINITY, M2 = -INFINITY;
+        for (int w = 0; w < DR_WARPS; ++w) {
+            M1 = fmaxf(M1, Ms[(w * R + r) * 4]);
+            M2 = fmaxf(M2, Ms[(w * R + r) * 4 + 2]);
+        }
+        float L1 = 0.f, L2 = 0.f, o1[NJ], o2[NJ];
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) {
-        const int d = lane + 32 * j;
-        if (d < DV) {
-            part[4 + d] = o1[j];
-            part[4 + DV + d] = o2[j];
+        for (int j = 0; j < NJ; ++j) o1[j] = o2[j] = 0.f;
+        for (int w = 0; w < DR_WARPS; ++w) {
+            const float* ms = Ms + (w * R + r) * 4;
+            if (ms[0] == -INFINITY) continue;    // a warp that saw no tile
+            const float f1 = expf(ms[0] - M1), f2 = expf(ms[2] - M2);
+            L1 = fmaf(ms[1], f1, L1);
+            L2 = fmaf(ms[3], f2, L2);
+#pragma unroll
+            for (int j = 0; j < NJ; ++j) {
+                const int d = lane + 32 * j;
+                if (d < DV) {
+                    o1[j] = fmaf(As[((w * R + r) * 2) * DV + d], f1, o1[j]);
+                    o2[j] = fmaf(As[((w * R + r) * 2 + 1) * DV + d], f2, o2[j]);
+                }
+            }
+        }
+        const int h = h0 + r;
+        if (splits == 1) {
+            da_finish<T, NJ>(a, t, h, o1, o2, L1, L2);
+            continue;
+        }
+        float* part = parts + ((t * a.H + h) * splits + share) * (long long)(4 + 2 * DV);
+        if (lane == 0) {
+            part[0] = M1;
+            part[1] = L1;
+            part[2] = M2;
+            part[3] = L2;
+        }
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) {
+            const int d = lane + 32 * j;
+            if (d < DV) {
+                part[4 + d] = o1[j];
+                part[4 + DV + d] = o2[j];
+            }
         }
     }
 }
@@ -506,9 +539,16 @@ diff_attn_merge_kernel(const DiffAttnArgs a, const float* __restrict__ parts, in
 template <typename T, int NJ>
 static int da_launch(const DiffAttnArgs& a, int rows_form, int max_len, float* parts, int splits, cudaStream_t st) {
     if (rows_form) {
-        const size_t smem = ((size_t)2 * a.D + DR_WARPS * 4 + (size_t)DR_WARPS * 2 * a.DV) * sizeof(float);
-        if (smem > 48 * 1024) cudaFuncSetAttribute(diff_attn_row_kernel<T, NJ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cm_launch(diff_attn_row_kernel<T, NJ>, dim3(a.H, a.T, splits), DR_WARPS * 32, smem, st, a, parts, splits);
+        // the query heads of a key/value head four at a time where their number allows it (the binding counts blocks by the same rule)
+        const int R = (a.H / a.G) % 4 == 0 ? 4 : 1;
+        const size_t smem = ((size_t)R * 2 * a.D + DR_WARPS * R * 4 + (size_t)DR_WARPS * R * 2 * a.DV) * sizeof(float);
+        if (R == 4) {
+            if (smem > 48 * 1024) cudaFuncSetAttribute(diff_attn_row_kernel<T, NJ, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            cm_launch(diff_attn_row_kernel<T, NJ, 4>, dim3(a.H / 4, a.T, splits), DR_WARPS * 32, smem, st, a, parts, splits);
+        } else {
+            if (smem > 48 * 1024) cudaFuncSetAttribute(diff_attn_row_kernel<T, NJ, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            cm_launch(diff_attn_row_kernel<T, NJ, 1>, dim3(a.H, a.T, splits), DR_WARPS * 32, smem, st, a, parts, splits);
+        }
         if (splits > 1) {
             CM_CHECK_LAUNCH();
             cm_launch(diff_attn_merge_kernel<T, NJ>, dim3(a.H, a.T), 32, 0, st, a, (const float*)parts, splits);

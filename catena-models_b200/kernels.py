@@ -958,11 +958,13 @@ class _DiffAttnArgs(ctypes.Structure):
 DIFF_ATTN_ROW_WARPS, DIFF_ATTN_MAX_SPLITS = 4, 16      # csrc/diffattn.cu: warps of a block of the rows form; most shares
 
 
-def diff_attn_splits(rows, H, keys, sm_count=148):
+def diff_attn_splits(rows, H, G, keys, sm_count=148):
     """Into how many shares the rows form cuts a row's visible keys (at most `keys` of them): enough blocks for two per
-    SM, while every warp still has a tile of 32 keys."""
+    SM, while every warp still has a tile of 32 keys.  A block takes four query heads of a key/value head together
+    where their number is a multiple of four."""
     tiles = -(-max(1, keys) // 32)
-    want = -(-2 * sm_count // max(1, rows * H))
+    blocks = rows * (H // 4 if (H // G) % 4 == 0 else H)
+    want = -(-2 * sm_count // max(1, blocks))
     return max(1, min(DIFF_ATTN_MAX_SPLITS, want, -(-tiles // DIFF_ATTN_ROW_WARPS)))
 
 

@@ -103,7 +103,7 @@ class DiffAttention(Mixer):
             # sized by the longest sequence that the step's class of lengths allows, so that a recording serves the class
             reach = kv.spec.entries(kv.spec.length_class(batch.max_end))
             keys = min(reach, self.window + self.keep_first) if self.window > 0 else reach
-            splits = kernels.diff_attn_splits(batch.T, H, keys)
+            splits = kernels.diff_attn_splits(batch.T, H, G, keys)
             if splits > 1:
                 parts = rt.scratch("diff_attn_parts", batch.T * H * splits * (4 + 2 * DV))
         kernels.diff_attn(ctx, q, proj[:, self.channels:], kv.pool, kv.pages, kv.ptab, batch, H, G, D, DV, self.window,

@@ -247,7 +247,7 @@ def _run_attention(q, k, v, window, keep, scale, lam, out_scale, eps, gate, rows
 
 
 @pytest.mark.parametrize("H, G, D, DV, T, window, keep", [
-    (4, 2, 16, 8, 150, 9, 3), (3, 1, 12, 20, 200, 70, 0), (2, 2, 8, 16, 90, 5, 11), (2, 1, 16, 24, 140, 64, 32),
+    (4, 2, 16, 8, 150, 9, 3), (3, 1, 12, 20, 200, 70, 0), (2, 2, 8, 16, 90, 5, 11), (4, 1, 16, 24, 140, 64, 32), (8, 2, 12, 20, 100, 30, 5),
     (2, 1, 8, 40, 100, 0, 0), (1, 1, 4, 4, 66, 1, 1), (2, 2, 64, 128, 130, 40, 20)])
 def test_two_maps_over_the_cache(H, G, D, DV, T, window, keep):
     q, k, v = _attention_case(6, H, G, D, DV, T, window, keep)

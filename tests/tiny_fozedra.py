@@ -63,7 +63,7 @@ TINY_C = model(96, 32, 1e-6, 0.5, [
 
 # one mechanism at a time
 ONLY_LIGHTNING = model(64, 40, 1e-6, 1.0, [lightning(2, 24, 40, None)])
-ONLY_ATTENTION = model(64, 32, 1e-6, 1.0, [attention(2, 1, 16, 24, 3, 0.3, 0.25, 12, 4, 8, mlp=None)])
+ONLY_ATTENTION = model(64, 32, 1e-6, 1.0, [attention(4, 1, 16, 24, 3, 0.3, 0.25, 12, 4, 8, mlp=None)])    # four query heads a key head
 ONLY_TAPS_ONE = model(64, 32, 1e-6, 1.0, [attention(2, 1, 16, 16, 1, 0.3, 0.25, 1000, 0, 8, mlp=None)])
 ONLY_FF = model(64, 24, 1e-6, 0.8, [lightning(1, 8, 8, dense(56))])
 
