@@ -55,61 +55,78 @@ template <typename T>
 __device__ __forceinline__ float tap_sum(const TapRotArgs& a, int c, int t, int pos, int p0, const float* st) {
     const int K = a.K;
     const float* w = a.taps + (long long)c * K;
-    float u[TR_MAXK];
-#pragma unroll
-    for (int j = 0; j < TR_MAXK; ++j)              // every tap's input is asked for before the first is used
-        u[j] = j < K ? tap_input<T>(a, c, t, pos, p0, pos - K + 1 + j, st) : 0.f;
     float y = 0.f;
-#pragma unroll
-    for (int j = 0; j < TR_MAXK; ++j)
-        if (j < K) y = fmaf(w[j], u[j], y);
+    if (pos - (K - 1) >= p0) {                     // every tap reads a row of this step: the usual case, kept short
+        const float bias = a.bias ? a.bias[c] : 0.f;
+        const T* u = (const T*)a.proj + (long long)(t - (K - 1)) * a.ldp + c;
+#pragma unroll 4
+        for (int j = 0; j < K; ++j) y = fmaf(w[j], to_f32(u[(long long)j * a.ldp]) + bias, y);
+        return y;
+    }
+    for (int j = 0; j < K; ++j) y = fmaf(w[j], tap_input<T>(a, c, t, pos, p0, pos - K + 1 + j, st), y);
     return y;
 }
 
-// One thread per token (grid x) and channel.  The state of a sequence is a ring of K rows: the projected row of
-// position s lies in row s % K.  A single token reads positions pos - K + 1 .. pos - 1 and then writes row
-// pos % K, which held position pos - K: nobody reads what it writes, so the state moves on in the same launch.
-template <typename T>
+// One thread per channel and TOK tokens (grid x walks the tokens TOK at a time).  The state of a sequence is a ring
+// of K rows: the projected row of position s lies in row s % K.  A single token reads positions pos - K + 1 ..
+// pos - 1 and then writes row pos % K, which held position pos - K: nobody reads what it writes, so the state moves
+// on in the same launch.  TOK > 1 (long steps): a thread forms its tokens' results side by side before it stores
+// any, so that their loads are in flight together; a block per token was bound by the waves of short blocks.
+template <typename T, int TOK>
 __global__ void __launch_bounds__(TR_THREADS)
 tap_rotate_store_kernel(const TapRotArgs a) {
     pdl_trigger();
     pdl_wait();
-    const int t = blockIdx.x;
-    const int b = a.tok_seq[t];
-    if (b < 0) return;
     const int C = a.QC + a.KC + a.VC;
     const int c = blockIdx.y * TR_THREADS + threadIdx.x;
     if (c >= C) return;
-    const int pos = a.tok_pos[t], p0 = a.seq_pos0[b];
-    float* st = a.state + (long long)a.seq_slot[b] * a.state_stride;
     const int half = a.rot >> 1;
-    float y = tap_sum<T>(a, c, t, pos, p0, st);
     const int cr = c < a.QC ? c : c - a.QC;           // channel within q, or within k | v
-    if (c < a.QC + a.KC && a.rate) {
-        const int e = cr % a.sub;
-        if (e < a.rot) {
-            const bool low = e < half;
-            const float other = tap_sum<T>(a, low ? c + half : c - half, t, pos, p0, st);
+    const int e = cr % max(a.sub, 1);
+    const bool turned = c < a.QC + a.KC && a.rate && e < a.rot, low = e < half;
+    float y[TOK], other[TOK];
+    int bs[TOK];
+#pragma unroll
+    for (int i = 0; i < TOK; ++i) {
+        const int t = blockIdx.x * TOK + i;
+        bs[i] = t < a.T ? a.tok_seq[t] : -1;
+        y[i] = other[i] = 0.f;
+        if (bs[i] < 0) continue;
+        const int pos = a.tok_pos[t], p0 = a.seq_pos0[bs[i]];
+        const float* st = a.state + (long long)a.seq_slot[bs[i]] * a.state_stride;
+        y[i] = tap_sum<T>(a, c, t, pos, p0, st);
+        if (turned) other[i] = tap_sum<T>(a, low ? c + half : c - half, t, pos, p0, st);
+    }
+#pragma unroll
+    for (int i = 0; i < TOK; ++i) {
+        const int t = blockIdx.x * TOK + i, b = bs[i];
+        if (b < 0) continue;
+        const int pos = a.tok_pos[t];
+        float v = y[i];
+        if (turned) {
             float sn, cs;
             sincosf((float)pos * a.rate[low ? e : e - half], &sn, &cs);
             sn *= a.mag;
             cs *= a.mag;
-            y = low ? y * cs - other * sn : y * cs + other * sn;
+            v = low ? v * cs - other[i] * sn : v * cs + other[i] * sn;
         }
-    }
-    if (c < a.QC) {
-        ((T*)a.q_out)[(long long)t * a.ldq + c] = from_f32<T>(y);
-    } else {
-        const int page = a.ptab[(long long)a.seq_slot[b] * a.ptab_stride + pos / PAGE_TOKENS], row = pos % PAGE_TOKENS;
-        if (cr < a.KC) {
-            const int g = cr / a.KW, off = cr - g * a.KW;
-            kv_tile((T*)a.pool, 0, a.pages, page, g, a.G, a.HDC)[(long long)row * a.HDC + off] = from_f32<T>(y);
+        if (c < a.QC) {
+            ((T*)a.q_out)[(long long)t * a.ldq + c] = from_f32<T>(v);
         } else {
-            const int cv = cr - a.KC, g = cv / a.DV, off = cv - g * a.DV;
-            kv_tile((T*)a.pool, 1, a.pages, page, g, a.G, a.HDC)[(long long)row * a.HDC + off] = from_f32<T>(y);
+            const int page = a.ptab[(long long)a.seq_slot[b] * a.ptab_stride + pos / PAGE_TOKENS], row = pos % PAGE_TOKENS;
+            if (cr < a.KC) {
+                const int g = cr / a.KW, off = cr - g * a.KW;
+                kv_tile((T*)a.pool, 0, a.pages, page, g, a.G, a.HDC)[(long long)row * a.HDC + off] = from_f32<T>(v);
+            } else {
+                const int cv = cr - a.KC, g = cv / a.DV, off = cv - g * a.DV;
+                kv_tile((T*)a.pool, 1, a.pages, page, g, a.G, a.HDC)[(long long)row * a.HDC + off] = from_f32<T>(v);
+            }
+        }
+        if (a.one_token_each && a.K > 1) {
+            float* st = a.state + (long long)a.seq_slot[b] * a.state_stride;
+            st[(long long)(pos % a.K) * C + c] = tap_input<T>(a, c, t, pos, a.seq_pos0[b], pos, st);
         }
     }
-    if (a.one_token_each && a.K > 1) st[(long long)(pos % a.K) * C + c] = tap_input<T>(a, c, t, pos, p0, pos, st);
 }
 
 // The state after a step of several tokens: the projected rows of the sequence's last K - 1 positions that the
@@ -143,13 +160,16 @@ extern "C" int cm_tap_rotate_store(int dt, const TapRotArgs* args, cudaStream_t 
     if ((a.KC || a.VC) && (!a.pool || a.KW > a.HDC || a.DV > a.HDC || a.KC != a.G * a.KW || a.VC != a.G * a.DV))
         CM_REFUSE("tap_rotate_store: %d key and %d value channels do not fit %d heads of %d", a.KC, a.VC, a.G, a.HDC);
     if (a.K > 1 && a.state_stride < (long long)a.K * C) CM_REFUSE("tap_rotate_store: a state row of %lld floats is too short", a.state_stride);
-    dim3 grid(a.T, (C + TR_THREADS - 1) / TR_THREADS), sgrid((C + TR_THREADS - 1) / TR_THREADS, a.B);
+    const bool many = a.T >= 512 && !a.one_token_each;               // long steps: four tokens a thread
+    dim3 grid(many ? (a.T + 3) / 4 : a.T, (C + TR_THREADS - 1) / TR_THREADS), sgrid((C + TR_THREADS - 1) / TR_THREADS, a.B);
     if (dt == DT_F32) {
-        cm_launch(tap_rotate_store_kernel<float>, grid, TR_THREADS, 0, st, a);
+        if (many) cm_launch(tap_rotate_store_kernel<float, 4>, grid, TR_THREADS, 0, st, a);
+        else cm_launch(tap_rotate_store_kernel<float, 1>, grid, TR_THREADS, 0, st, a);
         CM_CHECK_LAUNCH();
         if (!a.one_token_each && a.K > 1) cm_launch(tap_state_kernel<float>, sgrid, TR_THREADS, 0, st, a);
     } else if (dt == DT_BF16) {
-        cm_launch(tap_rotate_store_kernel<bf16>, grid, TR_THREADS, 0, st, a);
+        if (many) cm_launch(tap_rotate_store_kernel<bf16, 4>, grid, TR_THREADS, 0, st, a);
+        else cm_launch(tap_rotate_store_kernel<bf16, 1>, grid, TR_THREADS, 0, st, a);
         CM_CHECK_LAUNCH();
         if (!a.one_token_each && a.K > 1) cm_launch(tap_state_kernel<bf16>, sgrid, TR_THREADS, 0, st, a);
     } else

@@ -194,16 +194,26 @@ def _cached(pool, ptab, slot, length, kv, width):
 
 
 @pytest.mark.parametrize("H, G, D, DV, K, rot", [(4, 2, 16, 8, 4, 16), (3, 1, 12, 20, 5, 6), (2, 2, 8, 16, 2, 4), (2, 1, 16, 16, 1, 8),
-                                                 (2, 1, 8, 8, 3, 0)])
+                                                 (2, 1, 8, 8, 3, 0), (2, 1, 32, 24, 4, 16), (4, 2, 16, 40, 3, 0)])
 def test_taps_rotation_and_cache_write(H, G, D, DV, K, rot):
-    c = _taps_case(4, H, G, D, DV, K, rot, [70, 3, 130])
+    c = _taps_case(4, H, G, D, DV, K, rot, [70, 3, 530])    # the last one long enough for the form of long steps
     refs = [_taps_reference(c, i) for i in range(3)]
-    for cuts, slots in (([1000] * 3, [0, 1, 2]), ([7, 2, 64], [5, 0, 3]), ([1, 1, 1], [2, 6, 1]), ([2, 3, 129], [7, 4, 0])):
+    for cuts, slots in (([1000] * 3, [0, 1, 2]), ([7, 2, 64], [5, 0, 3]), ([1, 1, 1], [2, 6, 1]), ([2, 3, 517], [7, 4, 0])):
         qs, pool, ptab = _run_taps(c, cuts, slots)
         for i, n in enumerate(c["lengths"]):
             _close(qs[i], refs[i][0], 2e-5)
             _close(_cached(pool, ptab, slots[i], n, 0, 2 * D), refs[i][1], 2e-5)
             _close(_cached(pool, ptab, slots[i], n, 1, DV), refs[i][2], 3e-6)
+    # bfloat16 rows (the serving engine's): against the same statement on the rounded projections
+    for i in range(3):
+        c["proj"][i] = c["proj"][i].to(torch.bfloat16).float()
+    refs = [_taps_reference(c, i) for i in range(3)]
+    for cuts, slots in (([1000] * 3, [0, 1, 2]), ([1, 1, 1], [2, 6, 1])):
+        qs, pool, ptab = _run_taps(c, cuts, slots, dtype=torch.bfloat16)
+        for i, n in enumerate(c["lengths"]):
+            _close(qs[i], refs[i][0], 6e-3)
+            _close(_cached(pool, ptab, slots[i], n, 0, 2 * D), refs[i][1], 6e-3)
+            _close(_cached(pool, ptab, slots[i], n, 1, DV), refs[i][2], 6e-3)
 
 
 def _attention_case(seed, H, G, D, DV, T, window, keep, stand_out=None):
