@@ -550,13 +550,13 @@ def fozedra_config(size, vocab=VOCAB):
         heads=z["mem_heads"], dim=z["mem_dim"], vdim=z["mem_vdim"],
         decay=[round(1.0 - 2.0 ** (-2 - 6 * i / max(1, z["mem_heads"] - 1)), 6) for i in range(z["mem_heads"])]))
     att = lambda mlp, kv_from=None: dict(type="attention", mlp=mlp, mixer=dict(
-        heads=z["heads"] // 2, kv_heads=z["kv_heads"] // 2, dim=z["head"], vdim=2 * z["head"], conv=4, diff=0.3,
+        heads=z["heads"] // 2, kv_heads=z["kv_heads"] // 2, dim=z["head"], vdim=2 * z["head"], conv=4, diff=0.25,
         scale=z["head"] ** -0.5, mask=dict(size=1024, keep_first=64),
-        rot=dict(dims=z["head"] // 2, base=250000.0, scaling=dict(factor=8.0, original=2048, fast=32.0, slow=1.0)),
+        rot=dict(dims=z["head"] // 2, base=1000000.0, scaling=dict(factor=4.0, original=4096, fast=16.0, slow=2.0)),
         **({} if kv_from is None else dict(kv_from=kv_from))))
     dense = dict(kind="dense", ff=z["ff"])
     layers = [light(dense), att(dense), att(dense, 1), light(None), att(dense), att(dense, 4), light(dense), att(dense)]
-    return dict(architecture="Fozedra", vocab=vocab, width=z["width"], norm=dict(eps=1e-6), residual_mult=0.5, layers=layers)
+    return dict(architecture="Fozedra", vocab=vocab, width=z["width"], norm=dict(eps=1e-6), residual_mult=0.6, layers=layers)
 
 
 def lfm3_like_config(size, vocab=VOCAB):

@@ -60,7 +60,7 @@ def test_yarn_rates_against_the_plain_statement():
     import plain_fozedra as plain
     from catena_models_b200.parts import build_part
 
-    for dims, base, factor, original, fast, slow in ((24, 250000.0, 8.0, 2048, 32.0, 1.0), (6, 500.0, 2.0, 32, 8.0, 2.0),
+    for dims, base, factor, original, fast, slow in ((20, 40000.0, 6.0, 512, 24.0, 1.5), (6, 500.0, 2.0, 32, 8.0, 2.0),
                                                      (16, 10000.0, 4.0, 64, 16.0, 1.0)):
         part = build_part("position", "partial_yarn_rotary", dims=dims, theta=base, factor=factor, original=original,
                           fast=fast, slow=slow)

@@ -258,7 +258,7 @@ def _run_attention(q, k, v, window, keep, scale, lam, out_scale, eps, gate, rows
 
 @pytest.mark.parametrize("H, G, D, DV, T, window, keep", [
     (4, 2, 16, 8, 150, 9, 3), (3, 1, 12, 20, 200, 70, 0), (2, 2, 8, 16, 90, 5, 11), (4, 1, 16, 24, 140, 64, 32), (8, 2, 12, 20, 100, 30, 5),
-    (2, 1, 8, 40, 100, 0, 0), (1, 1, 4, 4, 66, 1, 1), (2, 2, 64, 128, 130, 40, 20)])
+    (2, 1, 8, 40, 100, 0, 0), (1, 1, 4, 4, 66, 1, 1), (2, 2, 64, 128, 130, 44, 18)])
 def test_two_maps_over_the_cache(H, G, D, DV, T, window, keep):
     q, k, v = _attention_case(6, H, G, D, DV, T, window, keep)
     gate = torch.randn(T, H, generator=torch.Generator().manual_seed(7))
@@ -276,7 +276,7 @@ def test_two_maps_over_the_cache(H, G, D, DV, T, window, keep):
 
 
 @pytest.mark.parametrize("H, G, D, DV, T, window, keep", [
-    (4, 2, 16, 16, 150, 9, 3), (3, 1, 32, 48, 200, 70, 0), (2, 2, 48, 96, 330, 40, 20), (2, 1, 64, 128, 260, 64, 32),
+    (4, 2, 16, 16, 150, 9, 3), (3, 1, 32, 48, 200, 70, 0), (2, 2, 48, 80, 330, 36, 12), (2, 1, 64, 128, 260, 64, 32),
     (2, 1, 128, 64, 140, 0, 0), (1, 1, 16, 32, 66, 1, 1), (2, 2, 80, 112, 200, 130, 70)])
 def test_two_maps_on_the_tensor_cores(H, G, D, DV, T, window, keep):
     """The bfloat16 tiles form on mma.sync against the plain statement on the same bfloat16 inputs: what is left is the
@@ -295,7 +295,7 @@ def test_two_maps_on_the_tensor_cores(H, G, D, DV, T, window, keep):
 
 
 @pytest.mark.parametrize("form", ["tiles", "rows", "mma"])
-@pytest.mark.parametrize("window, keep, T", [(40, 20, 300), (9, 3, 70), (64, 0, 200), (33, 40, 129)])
+@pytest.mark.parametrize("window, keep, T", [(48, 24, 300), (9, 3, 70), (64, 0, 200), (33, 40, 129)])
 def test_a_key_at_every_edge_decides_the_row(window, keep, T, form):
     """The last query's score with one key dwarfs the rest: just inside the window, just outside it, the last kept
     token, the first token that is not kept, a far key at a page border.  A mask that is one token off moves the result
