@@ -98,7 +98,7 @@ def test_whole_prompt(folders, plains, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "attention", "lightning"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "M", "attention", "lightning"])
 def test_prompt_then_token_by_token(folders, plains, name, dtype):
     """A prompt in one step, then tokens one by one (recorded decode steps from the second on): across a page
     border (64), past every window of these models, and from the very first token on."""
@@ -109,7 +109,7 @@ def test_prompt_then_token_by_token(folders, plains, name, dtype):
     check(run_alone(engine, tokens, [1]), ref, dtype)
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "M"])
 def test_portions_of_several_sizes(folders, plains, name):
     engine = model_for(folders, name, "float32").engine
     tokens = tiny.prompt(200, tiny.ALL[name]["vocab"], 3)
@@ -121,7 +121,7 @@ def test_portions_of_several_sizes(folders, plains, name):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "M"])
 def test_unequal_batch_against_each_alone(folders, plains, name, dtype):
     """Four requests of unequal length start together and are decoded together; the shorter ones end earlier and
     their slots and pages are taken by new requests while the others go on."""

@@ -61,13 +61,23 @@ TINY_C = model(96, 32, 1e-6, 0.5, [
     attention(2, 2, 8, 16, 2, 0.1, 0.4, 33, 2, 4, base=100.0, scaling=dict(factor=1.5, original=16, fast=4.0, slow=1.0),
               mlp=None)])
 
+# M: sizes that the tensor-core kernels take (head sizes that are multiples of 16, a width that is a multiple of 8): the
+# bfloat16 engine then runs the attention's prompt form on mma.sync and its products on the tensor-core and streaming kernels
+_M_ATT = dict(heads=4, kv_heads=2, dim=32, vdim=64, taps=3, diff=0.4, scale=0.18, size=72, keep=10, rot_dims=16, base=5000.0,
+              scaling=dict(factor=3.0, original=128, fast=20.0, slow=1.0))
+TINY_M = model(210, 128, 1e-6, 0.6, [
+    lightning(2, 32, 64, dense(256)),
+    attention(**_M_ATT, mlp=dense(192)),
+    attention(**_M_ATT, mlp=None, kv_from=1),
+    lightning(4, 16, 32, None)])
+
 # one mechanism at a time
 ONLY_LIGHTNING = model(64, 40, 1e-6, 1.0, [lightning(2, 24, 40, None)])
 ONLY_ATTENTION = model(64, 32, 1e-6, 1.0, [attention(4, 1, 16, 24, 3, 0.3, 0.25, 12, 4, 8, mlp=None)])    # four query heads a key head
 ONLY_TAPS_ONE = model(64, 32, 1e-6, 1.0, [attention(2, 1, 16, 16, 1, 0.3, 0.25, 1000, 0, 8, mlp=None)])
 ONLY_FF = model(64, 24, 1e-6, 0.8, [lightning(1, 8, 8, dense(56))])
 
-ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "lightning": ONLY_LIGHTNING, "attention": ONLY_ATTENTION,
+ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "M": TINY_M, "lightning": ONLY_LIGHTNING, "attention": ONLY_ATTENTION,
        "taps_one": ONLY_TAPS_ONE, "ff": ONLY_FF}
 
 
