@@ -110,6 +110,12 @@ class Reader:
             raise ConfigError(f"{self.where}: " + "; ".join(self.problems))
 
 
+def base_type(name):
+    """'mlstm_2' -> 'mlstm': a numeric suffix on a layer's type does not change the mixer."""
+    head, _, tail = name.rpartition("_")
+    return head if head and tail.isdigit() else name
+
+
 class _Prefixed:
     """A sub-section's problems land in its parent's list, with the section's path in front."""
 

@@ -12,7 +12,7 @@ from __future__ import annotations
 import dataclasses
 
 from ..csrc import limits
-from .base import ConfigError, Reader, section
+from .base import ConfigError, Reader, base_type, section
 
 MIXER_TYPES = ("lightning", "attention")
 
@@ -90,9 +90,9 @@ class FozedraConfig:
         if not isinstance(entry, dict) or not isinstance(entry.get("type"), str):
             r.problem(f"'{where}type' must be a string")
             return None
-        kind = entry["type"]
+        kind = base_type(entry["type"])
         if kind not in MIXER_TYPES:
-            r.problem(f"'{where}type' is '{kind}'; known mixers: {', '.join(MIXER_TYPES)}")
+            r.problem(f"'{where}type' is '{entry['type']}'; known mixers: {', '.join(MIXER_TYPES)}")
             return None
         m = section(r, entry, "mixer", where)
         mixer = None

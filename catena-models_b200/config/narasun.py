@@ -16,16 +16,10 @@ from __future__ import annotations
 import dataclasses
 
 from ..csrc import limits
-from .base import ConfigError, Reader, section as _section
+from .base import ConfigError, Reader, base_type, section as _section
 
 MIXER_TYPES = ("parallel", "mlstm")
 MLP_KINDS = ("dense", "moe")
-
-
-def base_type(name):
-    """'mlstm_2' -> 'mlstm': a numeric suffix does not change the mixer."""
-    head, _, tail = name.rpartition("_")
-    return head if head and tail.isdigit() else name
 
 
 @dataclasses.dataclass(frozen=True)

@@ -978,7 +978,7 @@ def diff_attn(ctx, q, gate, pool, pages, ptab, batch, H, G, D, DV, window, keep,
     `parts` of at least T * H * splits * (4 + 2 DV) elements between two launches; else tiles of queries, launched for
     batch.max_len rows a sequence, on the tensor cores with `tensor_cores` (bfloat16, head sizes that are multiples of 16
     up to 128: `diff_attn_mma_fits`)."""
-    if splits > 1 and (parts is None or parts.dtype != torch.float32 or parts.numel() < T_need(q, H, splits, DV)):
+    if splits > 1 and (parts is None or parts.dtype != torch.float32 or parts.numel() < _diff_attn_parts_floats(q, H, splits, DV)):
         raise KernelError("diff_attn: the shares' scratch is missing or too small")
     T = q.shape[0]
     if q.stride(1) != 1 or ctx.stride(1) != 1 or q.dtype != ctx.dtype or pool.dtype != q.dtype:
@@ -1006,7 +1006,8 @@ def diff_attn_mma_fits(D, DV, H, q_row, cache_entry):
     return D % 16 == 0 and DV % 16 == 0 and 0 < D <= 128 and 0 < DV <= 128 and q_row % 8 == 0 and cache_entry % 8 == 0
 
 
-def T_need(q, H, splits, DV):
+def _diff_attn_parts_floats(q, H, splits, DV):
+    """Floats of scratch between the two launches of the rows form: maxima, sums and value sums per row, head and share."""
     return q.shape[0] * H * splits * (4 + 2 * DV)
 
 
