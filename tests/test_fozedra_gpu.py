@@ -183,17 +183,35 @@ def test_long_decoding(folders, plains, name):
     check(run_alone(engine, tokens, [5]), exact(plains, name, tokens), "float32")
 
 
-def test_recorded_prompt_classes(folders, plains):
-    """Prompts of one class of shapes (rows rounded up to 64) run as a replayed recording from the second on, with rows of
-    padding behind the tokens; so do portions on top of held tokens."""
-    engine = model_for(folders, "A", "float32").engine
-    vocab = tiny.ALL["A"]["vocab"]
-    for n in (70, 75, 80, 90, 66):
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "M"])
+def test_recorded_prompt_classes(folders, plains, name, dtype):
+    """Prompts of one class of shapes (rows rounded up to 64, the same number of wanted places) run as a replayed
+    recording from the third on, with rows of padding behind the tokens; so do portions on top of held tokens.  The
+    lengths lie above 128, where lightning attention takes its chunked prompt form."""
+    engine = model_for(folders, name, dtype).engine
+    vocab = tiny.ALL[name]["vocab"]
+    before = len(engine._prompt_graphs)
+    got, ref = [], []
+    for n in (130, 150, 170, 192, 135, 129):
         tokens = tiny.prompt(n, vocab, 40 + n)
-        check(run_alone(engine, tokens, [n]), exact(plains, "A", tokens), "float32")
-    for n in (100, 110, 120):
+        (slot,) = engine.admit(1)
+        got.append(engine.step([slot], [tokens], [[n - 3, n - 1]]).float().cpu())
+        engine.release([slot])
+        full = exact(plains, name, tokens, dtype)
+        ref.append(tuple(f[[n - 3, n - 1]] for f in full) if isinstance(full, tuple) else full[[n - 3, n - 1]])
+    for n in (200, 230, 250, 210):
         tokens = tiny.prompt(n, vocab, 50 + n)
-        check(run_alone(engine, tokens, [40, n - 40]), exact(plains, "A", tokens), "float32")
+        (slot,) = engine.admit(1)
+        engine.step([slot], [tokens[:60]], [[]])
+        got.append(engine.step([slot], [tokens[60:]], [[0, n - 61]]).float().cpu())
+        engine.release([slot])
+        full = exact(plains, name, tokens, dtype)
+        ref.append(tuple(f[[60, n - 1]] for f in full) if isinstance(full, tuple) else full[[60, n - 1]])
+    engine.check_errors()
+    assert len(engine._prompt_graphs) >= before + 2          # both classes were recorded (and then replayed)
+    merged = tuple(torch.cat([r[i] for r in ref]) for i in range(2)) if isinstance(ref[0], tuple) else torch.cat(ref)
+    check(torch.cat(got), merged, dtype)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
